@@ -1,0 +1,1080 @@
+// fbw_b200.cu -- full-sum forward-backward (fast Baum-Welch) for B200 (sm_100a).
+//
+// Replaces the reference's host launcher and kernels (i6_native_ops/fbw/fbw_op.cu:17-153, 226-393)
+// behind the C ABI declared in include/fbw_b200.h.  Nothing here is a translation of that file:
+// the reference relaxes an unsorted global edge list once per frame with float atomicCAS loops
+// (5T+7 launches); this file sorts the automata once per call and then runs five kernels:
+//
+//   prepare   : validate, number states per sequence, sort edges by target state (forward list),
+//               by source state (backward list), by (sequence, emission) and by sequence.
+//   k_gather  : am_scores[t,b,emission] for the distinct emissions of each sequence -> compact
+//               score arrays (frame-major for the sweeps, 32-frame tiles for the posterior pass).
+//   k_sweep   : one persistent CTA per (sequence, direction); the automaton lives in shared memory,
+//               frames are stepped with one barrier each, next frames' scores arrive by cp.async.
+//   k_post    : time-parallel; one warp per (sequence, 32 frames), lane = frame.  Edge scores,
+//               the per-frame normaliser and the per-class posteriors.
+//   k_expand  : streams the (T,B,F) output: +inf rows with the few finite posteriors patched in.
+//
+// Arithmetic is kept in the reference's fp32 operation order wherever that order is deterministic
+// there, because scores grow with t (~2e4 at T=1500, one ulp = 2e-3) and any reassociation shows
+// up in the posteriors:
+//   * prob_add is fbw_op.cu:39-48 verbatim in meaning: -log1pf(expf(-|a-b|)) + fminf(a,b), +inf for
+//     a NaN difference; accurate libdevice expf/log1pf (no fast-math).
+//   * an edge's forward value is (alpha + weight) + score (fbw_op.cu:93); the edge score adds beta
+//     last (fbw_op.cu:96,99).
+//   * the normaliser is a left fold over the sequence's edges in ascending edge index
+//     (fbw_op.cu:115-118); state and class accumulations also run in ascending edge index (the
+//     reference's atomics have no defined order; with at most two terms the order is immaterial).
+
+#include "fbw_b200.h"
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <cub/cub.cuh>
+
+#include <cstdint>
+#include <cstdio>
+
+namespace {
+
+constexpr int kTile        = 32;   // frames per tile of the tiled layouts (= one lane per frame)
+constexpr int kGatherSlots = 256;  // classes per gather work item
+constexpr int kSegFloats   = 512;  // floats per output segment composed in shared memory
+constexpr int kMaxPerSeq   = 65535;
+
+typedef long long i64;
+
+// ---------------------------------------------------------------------------------------------
+// plan layout (device scratch owned by the caller)
+// ---------------------------------------------------------------------------------------------
+struct PlanLayout {
+    size_t header;
+    size_t state_key, skey, skey_out, siota, sorted_state, packed_of;            // [S]
+    size_t scount, ecount, state_off, edge_off, slot_off;                        // int[B+1]
+    size_t seq_T, start_l, end_l;                                                // int[B]
+    size_t ta_off, tg_off, gf_off, gu_off, pu_off;                               // i64[B+1]
+    size_t eiota, keyq, keyf, keyb, key32_out, qe, fe, be, me, slot_of_edge;     // [E]
+    size_t key64, key64_out;                                                     // u64[E]
+    size_t head, hs, m_ptr;                                                      // int[E+1]
+    size_t rowcnt_f, rowptr_f, rowcnt_b, rowptr_b;                               // int[S+1]
+    size_t fwd_rec, bwd_rec;                                                     // uint2[E]
+    size_t q_rec, m_rec;                                                         // int4[E]
+    size_t slot_emis;                                                            // int[E]
+    size_t cub_temp, cub_temp_bytes;
+    size_t total;
+};
+
+size_t cub_temp_need(i64 E, i64 S) {
+    size_t need = 0, b = 0;
+    int    nE = (int)(E > 0 ? E : 1), nS = (int)(S > 0 ? S : 1);
+    cub::DeviceRadixSort::SortPairs(nullptr, b, (const unsigned*)nullptr, (unsigned*)nullptr,
+                                    (const int*)nullptr, (int*)nullptr, nE > nS ? nE : nS);
+    need = b > need ? b : need;
+    cub::DeviceRadixSort::SortPairs(nullptr, b, (const unsigned long long*)nullptr,
+                                    (unsigned long long*)nullptr, (const int*)nullptr,
+                                    (int*)nullptr, nE);
+    need = b > need ? b : need;
+    cub::DeviceScan::ExclusiveSum(nullptr, b, (const int*)nullptr, (int*)nullptr,
+                                  (nE > nS ? nE : nS) + 1);
+    need = b > need ? b : need;
+    return need;
+}
+
+PlanLayout plan_layout(i64 B, i64 E, i64 S) {
+    PlanLayout L;
+    size_t     off  = 0;
+    auto       take = [&](size_t bytes) {
+        size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    size_t nE = (size_t)(E > 0 ? E : 1), nS = (size_t)S, nB = (size_t)B;
+    L.header       = take(sizeof(fbw_b200_summary));
+    L.state_key    = take(4 * nS);
+    L.skey         = take(4 * nS);
+    L.skey_out     = take(4 * nS);
+    L.siota        = take(4 * nS);
+    L.sorted_state = take(4 * nS);
+    L.packed_of    = take(4 * nS);
+    L.scount       = take(4 * (nB + 1));
+    L.ecount       = take(4 * (nB + 1));
+    L.state_off    = take(4 * (nB + 1));
+    L.edge_off     = take(4 * (nB + 1));
+    L.slot_off     = take(4 * (nB + 1));
+    L.seq_T        = take(4 * nB);
+    L.start_l      = take(4 * nB);
+    L.end_l        = take(4 * nB);
+    L.ta_off       = take(8 * (nB + 1));
+    L.tg_off       = take(8 * (nB + 1));
+    L.gf_off       = take(8 * (nB + 1));
+    L.gu_off       = take(8 * (nB + 1));
+    L.pu_off       = take(8 * (nB + 1));
+    L.eiota        = take(4 * nE);
+    L.keyq         = take(4 * nE);
+    L.keyf         = take(4 * nE);
+    L.keyb         = take(4 * nE);
+    L.key32_out    = take(4 * nE);
+    L.qe           = take(4 * nE);
+    L.fe           = take(4 * nE);
+    L.be           = take(4 * nE);
+    L.me           = take(4 * nE);
+    L.slot_of_edge = take(4 * nE);
+    L.key64        = take(8 * nE);
+    L.key64_out    = take(8 * nE);
+    L.head         = take(4 * (nE + 1));
+    L.hs           = take(4 * (nE + 1));
+    L.m_ptr        = take(4 * (nE + 1));
+    L.rowcnt_f     = take(4 * (nS + 1));
+    L.rowptr_f     = take(4 * (nS + 1));
+    L.rowcnt_b     = take(4 * (nS + 1));
+    L.rowptr_b     = take(4 * (nS + 1));
+    L.fwd_rec      = take(8 * nE);
+    L.bwd_rec      = take(8 * nE);
+    L.q_rec        = take(16 * nE);
+    L.m_rec        = take(16 * nE);
+    L.slot_emis    = take(4 * nE);
+    L.cub_temp_bytes = cub_temp_need(E, S);
+    L.cub_temp       = take(L.cub_temp_bytes);
+    L.total          = off;
+    return L;
+}
+
+template <typename T>
+T* at(void* base, size_t off) {
+    return reinterpret_cast<T*>(reinterpret_cast<char*>(base) + off);
+}
+template <typename T>
+const T* at(const void* base, size_t off) {
+    return reinterpret_cast<const T*>(reinterpret_cast<const char*>(base) + off);
+}
+
+int bits_for(unsigned long long maxval) {
+    int b = 1;
+    while (b < 64 && (maxval >> b) != 0) b++;
+    return b;
+}
+
+// ---------------------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------------------
+
+// Log-semiring sum of two negative-log values; same expression as the reference's prob_add
+// (i6_native_ops/fbw/fbw_op.cu:39-48) so results round identically.
+__device__ __forceinline__ float prob_add(float a, float b) {
+    float diff = a - b;
+    if (isnan(diff)) {
+        return CUDART_INF_F;
+    }
+    return -log1pf(expf(-fabsf(diff))) + fminf(a, b);
+}
+
+// largest b in [0,B) with off[b] <= u, given off[0] <= u < off[B]
+__device__ __forceinline__ int find_seq(const i64* __restrict__ off, int B, i64 u) {
+    int lo = 0, hi = B;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (off[mid] <= u) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    return lo;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// prepare kernels
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void claim_state(int* state_key, int* scount, int s, int q,
+                                            fbw_b200_summary* hdr) {
+    int old = atomicCAS(&state_key[s], -1, q);
+    if (old == -1) {
+        atomicAdd(&scount[q], 1);
+    } else if (old != q) {
+        atomicOr((unsigned long long*)&hdr->error, (unsigned long long)FBW_B200_ERR_SHARED_STATE);
+    }
+}
+
+// one thread per edge, then one per sequence: range checks, edge counts, state ownership
+__global__ void k_mark(const int* __restrict__ edges, const int* __restrict__ start_end, i64 E,
+                       i64 B, i64 S, i64 F, int* state_key, int* scount, int* ecount,
+                       fbw_b200_summary* hdr) {
+    i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < E) {
+        int fr = edges[idx], to = edges[E + idx], em = edges[2 * E + idx], sq = edges[3 * E + idx];
+        unsigned long long err = 0;
+        if (fr < 0 || fr >= S || to < 0 || to >= S) err |= FBW_B200_ERR_STATE_RANGE;
+        if (em < 0 || em >= F) err |= FBW_B200_ERR_EMISSION_RANGE;
+        if (sq < 0 || sq >= B) err |= FBW_B200_ERR_SEQ_RANGE;
+        if (err) {
+            atomicOr((unsigned long long*)&hdr->error, err);
+            return;
+        }
+        atomicAdd(&ecount[sq], 1);
+        claim_state(state_key, scount, fr, sq, hdr);
+        claim_state(state_key, scount, to, sq, hdr);
+    } else if (idx < E + B) {
+        int b = (int)(idx - E);
+        int s0 = start_end[b], s1 = start_end[B + b];
+        if (s0 < 0 || s0 >= S || s1 < 0 || s1 >= S) {
+            atomicOr((unsigned long long*)&hdr->error, (unsigned long long)FBW_B200_ERR_START_END);
+            return;
+        }
+        claim_state(state_key, scount, s0, b, hdr);
+        claim_state(state_key, scount, s1, b, hdr);
+    }
+}
+
+// single block: exclusive scans of the per-sequence state and edge counts; effective lengths
+__global__ void __launch_bounds__(1024) k_off1(const int* __restrict__ scount,
+                                              const int* __restrict__ ecount,
+                                              const int* __restrict__ seq_lens, int B, i64 T,
+                                              int* state_off, int* edge_off, int* seq_T) {
+    typedef cub::BlockScan<int, 1024> Scan;
+    __shared__ typename Scan::TempStorage tmp;
+    __shared__ int carry[2];
+    if (threadIdx.x == 0) carry[0] = carry[1] = 0;
+    __syncthreads();
+    for (int base = 0; base < B; base += 1024) {
+        int  b  = base + threadIdx.x;
+        bool ok = b < B;
+        int  v[2] = {ok ? scount[b] : 0, ok ? ecount[b] : 0};
+        int* dst[2] = {state_off, edge_off};
+        for (int k = 0; k < 2; k++) {
+            int ex, agg;
+            Scan(tmp).ExclusiveSum(v[k], ex, agg);
+            if (ok) dst[k][b] = carry[k] + ex;
+            __syncthreads();
+            if (threadIdx.x == 0) carry[k] += agg;
+            __syncthreads();
+        }
+        if (ok) {
+            // a sequence contributes only if 1 <= seq_len <= T: the backward seed is placed at
+            // frame seq_len (fbw_op.cu:61-69 with the loop of 339-353), which never happens otherwise
+            int n    = seq_lens[b];
+            seq_T[b] = (n >= 1 && (i64)n <= T) ? n : 0;
+        }
+    }
+    if (threadIdx.x == 0) {
+        state_off[B] = carry[0];
+        edge_off[B]  = carry[1];
+    }
+}
+
+__global__ void k_statekeys(const int* __restrict__ state_key, i64 S, int B, unsigned* skey,
+                            int* siota) {
+    i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s < S) {
+        int k    = state_key[s];
+        skey[s]  = k < 0 ? (unsigned)B : (unsigned)k;
+        siota[s] = (int)s;
+    }
+}
+
+__global__ void k_packed(const int* __restrict__ sorted_state, i64 S, int* packed_of) {
+    i64 p = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < S) packed_of[sorted_state[p]] = (int)p;
+}
+
+__global__ void k_edgekeys(const int* __restrict__ edges, i64 E, i64 F,
+                           const int* __restrict__ packed_of, unsigned* keyq, unsigned* keyf,
+                           unsigned* keyb, unsigned long long* key64, int* eiota, int* rowcnt_f,
+                           int* rowcnt_b, const fbw_b200_summary* hdr) {
+    if (hdr->error) return;
+    i64 e = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < E) {
+        int fr = edges[e], to = edges[E + e], em = edges[2 * E + e], sq = edges[3 * E + e];
+        int pf = packed_of[fr], pt = packed_of[to];
+        keyq[e]  = (unsigned)sq;
+        keyf[e]  = (unsigned)pt;
+        keyb[e]  = (unsigned)pf;
+        key64[e] = (unsigned long long)sq * (unsigned long long)F + (unsigned long long)em;
+        eiota[e] = (int)e;
+        atomicAdd(&rowcnt_f[pt], 1);
+        atomicAdd(&rowcnt_b[pf], 1);
+    }
+}
+
+__global__ void k_heads(const unsigned long long* __restrict__ key64s, i64 E, int* head) {
+    i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < E) {
+        head[i] = (i == 0 || key64s[i] != key64s[i - 1]) ? 1 : 0;
+    } else if (i == E) {
+        head[i] = 0;
+    }
+}
+
+// hs[i] = number of class-group heads before position i of the (sequence, emission)-sorted list
+__global__ void k_slots(const unsigned long long* __restrict__ key64s, const int* __restrict__ me,
+                        const int* __restrict__ head, const int* __restrict__ hs, i64 E, i64 F,
+                        int* slot_of_edge, int* slot_emis, int* m_ptr,
+                        const fbw_b200_summary* hdr) {
+    if (hdr->error) return;
+    i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < E) {
+        int g = hs[i] + head[i] - 1;  // global slot of this edge
+        if (head[i]) {
+            slot_emis[g] = (int)(key64s[i] % (unsigned long long)F);
+            m_ptr[g]     = (int)i;
+        }
+        slot_of_edge[me[i]] = g;
+    } else if (i == E) {
+        m_ptr[hs[E]] = (int)E;
+    }
+}
+
+// single block: everything per sequence that needs the slot counts; offsets of the run arrays
+__global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off,
+                                              const int* __restrict__ edge_off,
+                                              const int* __restrict__ hs,
+                                              const int* __restrict__ seq_T,
+                                              const int* __restrict__ start_end,
+                                              const int* __restrict__ packed_of, int B, i64 T,
+                                              i64 F, i64 E, i64 S, int* slot_off, int* start_l,
+                                              int* end_l, i64* ta_off, i64* tg_off, i64* gf_off,
+                                              i64* gu_off, i64* pu_off, fbw_b200_summary* hdr) {
+    typedef cub::BlockScan<i64, 1024> Scan;
+    __shared__ typename Scan::TempStorage tmp;
+    __shared__ i64 carry[6];
+    __shared__ int smax[4];
+    if (threadIdx.x < 6) carry[threadIdx.x] = 0;
+    if (threadIdx.x < 4) smax[threadIdx.x] = 0;
+    __syncthreads();
+    const bool bad = hdr->error != 0;
+    for (int base = 0; base < B; base += 1024) {
+        int  b  = base + threadIdx.x;
+        bool ok = b < B;
+        i64  v[6] = {0, 0, 0, 0, 0, 0};
+        if (ok) {
+            int Sb = state_off[b + 1] - state_off[b];
+            int Eb = edge_off[b + 1] - edge_off[b];
+            int so = hs[edge_off[b]];
+            int Db = hs[edge_off[b + 1]] - so;
+            int Te = seq_T[b];
+            int nt = (Te + kTile - 1) / kTile;
+            int Dp = (Db + 3) & ~3;
+            slot_off[b] = so;
+            if (!bad) {
+                start_l[b] = packed_of[start_end[b]] - state_off[b];
+                end_l[b]   = packed_of[start_end[B + b]] - state_off[b];
+            }
+            v[0] = (i64)nt * Sb * kTile;
+            v[1] = (i64)nt * Db * kTile;
+            v[2] = (i64)Te * Dp;
+            v[3] = (i64)nt * ((Db + kGatherSlots - 1) / kGatherSlots);
+            v[4] = nt;
+            v[5] = Te;
+            atomicMax(&smax[0], Sb);
+            atomicMax(&smax[1], Eb);
+            atomicMax(&smax[2], Db);
+            atomicMax(&smax[3], Te);
+        }
+        i64* dst[5] = {ta_off, tg_off, gf_off, gu_off, pu_off};
+        for (int k = 0; k < 6; k++) {
+            i64 ex, agg;
+            Scan(tmp).ExclusiveSum(v[k], ex, agg);
+            if (ok && k < 5) dst[k][b] = carry[k] + ex;
+            __syncthreads();
+            if (threadIdx.x == 0) carry[k] += agg;
+            __syncthreads();
+        }
+    }
+    if (threadIdx.x == 0) {
+        slot_off[B] = hs[E];
+        ta_off[B] = carry[0];
+        tg_off[B] = carry[1];
+        gf_off[B] = carry[2];
+        gu_off[B] = carry[3];
+        pu_off[B] = carry[4];
+        hdr->T = T; hdr->B = B; hdr->F = F; hdr->E = E; hdr->S = S;
+        hdr->state_floats = carry[0];
+        hdr->tiled_floats = carry[1];
+        hdr->frame_floats = carry[2];
+        hdr->gather_units = carry[3];
+        hdr->post_units   = carry[4];
+        hdr->sum_len      = carry[5];
+        hdr->num_slots    = hs[E];
+        hdr->max_states = smax[0];
+        hdr->max_edges  = smax[1];
+        hdr->max_slots  = smax[2];
+        hdr->max_len    = smax[3];
+        if (smax[0] > kMaxPerSeq || smax[2] > kMaxPerSeq) {
+            hdr->error |= FBW_B200_ERR_SEQ_TOO_LARGE;
+        }
+    }
+}
+
+// the four sorted edge lists as records with sequence-local state ids and class slots
+__global__ void k_records(const int* __restrict__ edges, const float* __restrict__ weights, i64 E,
+                          const int* __restrict__ packed_of, const int* __restrict__ state_off,
+                          const int* __restrict__ slot_off, const int* __restrict__ slot_of_edge,
+                          const int* __restrict__ qe, const int* __restrict__ fe,
+                          const int* __restrict__ be, const int* __restrict__ me, uint2* fwd_rec,
+                          uint2* bwd_rec, int4* q_rec, int4* m_rec,
+                          const fbw_b200_summary* hdr) {
+    if (hdr->error) return;
+    i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= E) return;
+    auto rec = [&](int e, int& fr, int& to, int& sl, float& w) {
+        int sq = edges[3 * E + e];
+        fr = packed_of[edges[e]] - state_off[sq];
+        to = packed_of[edges[E + e]] - state_off[sq];
+        sl = slot_of_edge[e] - slot_off[sq];
+        w  = weights[e];
+    };
+    int   fr, to, sl;
+    float w;
+    rec(fe[i], fr, to, sl, w);
+    fwd_rec[i] = make_uint2((unsigned)fr | ((unsigned)sl << 16), __float_as_uint(w));
+    rec(be[i], fr, to, sl, w);
+    bwd_rec[i] = make_uint2((unsigned)to | ((unsigned)sl << 16), __float_as_uint(w));
+    rec(qe[i], fr, to, sl, w);
+    q_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
+    rec(me[i], fr, to, sl, w);
+    m_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
+}
+
+// ---------------------------------------------------------------------------------------------
+// run kernels
+// ---------------------------------------------------------------------------------------------
+struct RunArgs {
+    const float* am;
+    float*       out;
+    float*       sums;
+    float*       loss2;
+    float *A, *Bt, *Gt, *Gf, *P;
+    const int *state_off, *edge_off, *slot_off, *seq_T, *start_l, *end_l;
+    const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off;
+    const int *rowptr_f, *rowptr_b;
+    const uint2 *fwd_rec, *bwd_rec;
+    const int4 *q_rec, *m_rec;
+    const int *m_ptr, *slot_emis;
+    i64 T, B, F;
+    i64 gather_units, post_units;
+};
+
+// Gather am_scores[t,b,emission] for the distinct emissions ("slots", ascending emission id) of
+// each sequence.  Work item = (sequence, 32-frame tile, 256 slots).  Two copies are written:
+//   Gf  frame-major  [t][slot]           (rows padded to 4 floats)  -- read by the sweeps
+//   Gt  tiled        [t/32][slot][t%32]                              -- read by k_post, lane = frame
+__global__ void __launch_bounds__(256) k_gather(RunArgs a) {
+    __shared__ float tile[kTile][kGatherSlots + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int B = (int)a.B;
+    for (i64 u = blockIdx.x; u < a.gather_units; u += gridDim.x) {
+        const int b   = find_seq(a.gu_off, B, u);
+        const int r   = (int)(u - a.gu_off[b]);
+        const int so  = a.slot_off[b];
+        const int Db  = a.slot_off[b + 1] - so;
+        const int Dp  = (Db + 3) & ~3;
+        const int nch = (Db + kGatherSlots - 1) / kGatherSlots;
+        const int k = r / nch, c = r % nch;
+        const int Te = a.seq_T[b];
+        const int d0 = c * kGatherSlots;
+        const int nd = min(kGatherSlots, Db - d0);
+        const int* __restrict__ emis = a.slot_emis + so + d0;
+        float* __restrict__ gf = a.Gf + a.gf_off[b];
+        float* __restrict__ gt = a.Gt + a.tg_off[b] + ((i64)k * Db + d0) * kTile;
+
+        int em[kGatherSlots / 32];
+#pragma unroll
+        for (int j = 0; j < kGatherSlots / 32; j++) {
+            int dd = lane + 32 * j;
+            em[j]  = dd < nd ? emis[dd] : 0;
+        }
+        for (int f = warp; f < kTile; f += 8) {
+            const int  t     = k * kTile + f;
+            const bool valid = t < Te;
+            const float* __restrict__ row = a.am + ((i64)t * B + b) * a.F;
+            float v[kGatherSlots / 32];
+#pragma unroll
+            for (int j = 0; j < kGatherSlots / 32; j++) {
+                int dd = lane + 32 * j;
+                v[j]   = (valid && dd < nd) ? __ldg(row + em[j]) : CUDART_INF_F;
+            }
+#pragma unroll
+            for (int j = 0; j < kGatherSlots / 32; j++) {
+                int dd = lane + 32 * j;
+                if (dd < nd) {
+                    tile[f][dd] = v[j];
+                    if (valid) gf[(i64)t * Dp + d0 + dd] = v[j];
+                }
+            }
+            if (valid && c == nch - 1) {
+                for (int dd = Db + lane; dd < Dp; dd += 32) gf[(i64)t * Dp + dd] = 0.f;
+            }
+        }
+        __syncthreads();
+        for (int dd = warp; dd < nd; dd += 8) gt[(i64)dd * kTile + lane] = tile[lane][dd];
+        __syncthreads();
+    }
+}
+
+// One persistent CTA per (sequence, direction).  Shared memory holds the sequence's sorted edge list
+// (target-sorted for the forward sweep, source-sorted for the backward one), two state-score
+// vectors and a ring of RING gathered-score rows filled by cp.async a few frames ahead.
+// Forward: alpha_0 = {start: 0}; alpha_{t+1}(s) = fold over in-edges, ascending edge index, of
+// (alpha_t(from) + w) + score_t(emission).  alpha_t for t < len is stored (tiled) for k_post.
+// Backward: beta_len = {end: 0}; beta_t(s) = fold over out-edges of (beta_{t+1}(to) + w) + score_t;
+// the array stores beta_{t+1} at frame index t, which is what the edge score of frame t needs.
+// Replaces set_start_states / init_bwd_state_buffer / next_frame / fill_array and the two host loops
+// (fbw_op.cu:17-29, 61-102, 297-353).
+template <int RING>
+__global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int item = blockIdx.x;
+    const int b    = item >> 1;
+    const bool fwd = (item & 1) == 0;
+    const int  Te  = a.seq_T[b];
+    if (Te == 0) return;
+    const int s0 = a.state_off[b], Sb = a.state_off[b + 1] - s0;
+    const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
+    const int Db = a.slot_off[b + 1] - a.slot_off[b];
+    const int Dp = (Db + 3) & ~3;
+    const int NT = blockDim.x, tid = threadIdx.x;
+
+    float* ring = reinterpret_cast<float*>(smem_raw);                       // RING * dpmax
+    float* buf0 = ring + (size_t)(RING > 0 ? RING : 0) * dpmax;             // smax
+    float* buf1 = buf0 + smax;                                              // smax
+    int*   rp   = reinterpret_cast<int*>(buf1 + smax);                      // smax + 1 (+ pad)
+    uint2* recs_s = reinterpret_cast<uint2*>(rp + ((smax + 2) & ~1));
+
+    const int* __restrict__ rowptr = (fwd ? a.rowptr_f : a.rowptr_b) + s0;
+    const uint2* __restrict__ recs_g = (fwd ? a.fwd_rec : a.bwd_rec) + e0;
+    for (int s = tid; s <= Sb; s += NT) rp[s] = rowptr[s] - e0;
+    const uint2* recs = recs_g;
+    if (edges_in_smem) {
+        for (int i = tid; i < Eb; i += NT) recs_s[i] = recs_g[i];
+        recs = recs_s;
+    }
+    const int seed = fwd ? a.start_l[b] : a.end_l[b];
+    for (int s = tid; s < Sb; s += NT) buf0[s] = (s == seed) ? 0.f : CUDART_INF_F;
+
+    const float* __restrict__ gf = a.Gf + a.gf_off[b];
+    float* __restrict__ dst = (fwd ? a.A : a.Bt) + a.ta_off[b];
+    const int nvec = Dp >> 2;
+    const int step = fwd ? 1 : -1;
+    const int t_first = fwd ? 0 : Te - 1;
+    // frames whose scores are consumed: forward 0..Te-2, backward Te-1..1
+    auto issue = [&](int j) {  // j-th consumed frame
+        if (RING > 0) {
+            int t = t_first + step * j;
+            if (j < Te - 1) {
+                float*       d = ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax;
+                const float* g = gf + (i64)t * Dp;
+                for (int i = tid; i < nvec; i += NT) cp_async16(d + 4 * i, g + 4 * i);
+            }
+            cp_async_commit();
+        }
+    };
+    if (RING > 0) {
+#pragma unroll
+        for (int j = 0; j < RING - 1; j++) issue(j);
+    }
+
+    constexpr int kWait = RING > 1 ? RING - 2 : 0;
+    float* cur = buf0;
+    float* nxt = buf1;
+    for (int j = 0; j < Te; j++) {
+        const int t = t_first + step * j;
+        if (RING > 0) cp_async_wait<kWait>();
+        __syncthreads();
+        if (RING > 0) issue(j + RING - 1);
+        // record this frame's state scores (tiled layout: [t/32][state][t%32])
+        float* drow = dst + ((i64)(t >> 5) * Sb) * kTile + (t & 31);
+        for (int s = tid; s < Sb; s += NT) drow[(i64)s * kTile] = cur[s];
+        if (j == Te - 1) break;
+        const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
+                                  : gf + (i64)t * Dp;
+        for (int s = tid; s < Sb; s += NT) {
+            float acc = CUDART_INF_F;
+            const int i1 = rp[s + 1];
+            for (int i = rp[s]; i < i1; i++) {
+                const uint2 r  = recs[i];
+                const float pv = cur[r.x & 0xffffu];
+                if (!isinf(pv)) {
+                    const float val = (pv + __uint_as_float(r.y)) + g[r.x >> 16];
+                    acc = prob_add(acc, val);
+                }
+            }
+            nxt[s] = acc;
+        }
+        float* tmp = cur;
+        cur = nxt;
+        nxt = tmp;
+    }
+    if (RING > 0) cp_async_wait<0>();
+}
+
+// Edge scores, normaliser and class posteriors; one warp per (sequence, 32-frame tile), lane = frame.
+// For frame t:  x_e = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)   (fbw_op.cu:93-100)
+//   sum  = left fold of prob_add over the sequence's edges in ascending edge index (fbw_op.cu:115-118)
+//   sums[t,b] = isinf(sum) ? 0 : sum                                              (fbw_op.cu:120-129)
+//   post[t][slot] = fold over the slot's edges of (x_e - sum)                     (fbw_op.cu:131-153)
+// prob_add(acc, +inf) == acc exactly, so dead edges are skipped without changing any bit.
+__global__ void __launch_bounds__(128) k_post(RunArgs a) {
+    __shared__ float stage[4][kTile][kTile + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int B = (int)a.B;
+    float (*st)[kTile + 1] = stage[warp];
+    for (i64 u = (i64)blockIdx.x * 4 + warp; u < a.post_units; u += (i64)gridDim.x * 4) {
+        const int b  = find_seq(a.pu_off, B, u);
+        const int k  = (int)(u - a.pu_off[b]);
+        const int Sb = a.state_off[b + 1] - a.state_off[b];
+        const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
+        const int so = a.slot_off[b], Db = a.slot_off[b + 1] - so;
+        const int Dp = (Db + 3) & ~3;
+        const int Te = a.seq_T[b];
+        const int t  = k * kTile + lane;
+        const bool valid = t < Te;
+        const float* __restrict__ Ab = a.A + a.ta_off[b] + (i64)k * Sb * kTile + lane;
+        const float* __restrict__ Bb = a.Bt + a.ta_off[b] + (i64)k * Sb * kTile + lane;
+        const float* __restrict__ Gb = a.Gt + a.tg_off[b] + (i64)k * Db * kTile + lane;
+        const int4* __restrict__ q = a.q_rec + e0;
+
+        auto edge_score = [&](const int4 r) -> float {
+            float al = valid ? Ab[(i64)r.x * kTile] : CUDART_INF_F;
+            float be = valid ? Bb[(i64)r.y * kTile] : CUDART_INF_F;
+            float g  = valid ? Gb[(i64)r.z * kTile] : CUDART_INF_F;
+            // the reference writes +inf for an edge whose source (forward) or target (backward)
+            // state is unreachable (fbw_op.cu:82-85) before any addition
+            if (isinf(al) || isinf(be)) return CUDART_INF_F;
+            return ((al + __int_as_float(r.w)) + g) + be;
+        };
+
+        float acc = CUDART_INF_F;
+        for (int i = 0; i < Eb; i++) {
+            const float x = edge_score(q[i]);
+            if (!(x == CUDART_INF_F)) acc = prob_add(acc, x);
+        }
+        if (valid) a.sums[(i64)t * B + b] = isinf(acc) ? 0.f : acc;
+
+        const int4* __restrict__ m  = a.m_rec;
+        const int* __restrict__ mp  = a.m_ptr + so;
+        float* __restrict__ Pb      = a.P + a.gf_off[b];
+        for (int d0 = 0; d0 < Db; d0 += kTile) {
+            const int nd = min(kTile, Db - d0);
+            for (int dd = 0; dd < nd; dd++) {
+                float p = CUDART_INF_F;
+                const int j1 = mp[d0 + dd + 1];
+                for (int j = mp[d0 + dd]; j < j1; j++) {
+                    const float x = edge_score(m[j]);
+                    p = prob_add(p, x - acc);
+                }
+                st[dd][lane] = p;
+            }
+            __syncwarp();
+            // transpose: row r of the tile gets its nd posteriors as one contiguous write
+            for (int r = 0; r < kTile; r++) {
+                const int tr = k * kTile + r;
+                if (tr < Te && lane < nd) Pb[(i64)tr * Dp + d0 + lane] = st[lane][r];
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// Stream the (T,B,F) output: every row is +inf except the sequence's class slots, which get the
+// posteriors k_post left in P (frame-major, ascending emission id); rows at or past seq_len are all
+// +inf.  One warp per row; the row is composed 512 floats at a time in shared memory and stored as
+// 16-byte vectors.  Rows start at arbitrary 4-byte offsets (F need not be a multiple of 4), so each
+// row is split into a scalar head, a 16-byte aligned body and a scalar tail.  One pass over the
+// output instead of the reference's zeros_like + fill + atomics (fbw_op.cu:230, 366-378).
+__global__ void __launch_bounds__(256) k_expand(RunArgs a) {
+    __shared__ __align__(16) float segs[8][kSegFloats];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int B = (int)a.B;
+    const i64 F = a.F;
+    float* seg = segs[warp];
+    for (int i = lane; i < kSegFloats; i += 32) seg[i] = CUDART_INF_F;
+    __syncwarp();
+    const i64 rows = a.T * a.B;
+    for (i64 r = (i64)blockIdx.x * 8 + warp; r < rows; r += (i64)gridDim.x * 8) {
+        const int  t  = (int)(r / B);
+        const int  b  = (int)(r - (i64)t * B);
+        const bool valid = t < a.seq_T[b];
+        const int  so = a.slot_off[b];
+        const int  Db = valid ? a.slot_off[b + 1] - so : 0;
+        const int  Dp = ((a.slot_off[b + 1] - so) + 3) & ~3;
+        const int* __restrict__ emis = a.slot_emis + so;
+        const float* __restrict__ Pr = a.P + a.gf_off[b] + (i64)t * Dp;
+        const i64 rbase = r * F;
+        float* __restrict__ row = a.out + rbase;
+        const int head = (int)min((i64)((4 - (rbase & 3)) & 3), F);
+        const i64 nvec = (F - head) >> 2;
+        const i64 body_end = head + 4 * nvec;
+
+        int dlo = 0;  // next unconsumed slot; slots are in ascending emission id
+        // head scalars
+        if (head > 0) {
+            float v = CUDART_INF_F;
+            // at most 3 columns: the first slots may fall here
+            for (int d = 0; d < Db && d < 3; d++) {
+                int e = emis[d];
+                if (e == lane && e < head) v = Pr[d];
+            }
+            if (lane < head) row[lane] = v;
+            while (dlo < Db && emis[dlo] < head) dlo++;
+        }
+        // aligned body
+        for (i64 cs = head; cs < body_end; cs += kSegFloats) {
+            const i64 ce = min(cs + (i64)kSegFloats, body_end);
+            const int dstart = dlo;
+            int n;
+            do {  // patch the slots of this segment
+                const int d  = dlo + lane;
+                const int e  = d < Db ? emis[d] : 0x7fffffff;
+                const bool in = e < ce;
+                if (in) seg[e - cs] = Pr[d];
+                n = __popc(__ballot_sync(0xffffffffu, in));
+                dlo += n;
+            } while (n == 32);
+            __syncwarp();
+            const int nv = (int)((ce - cs) >> 2);
+            float4* __restrict__ dst4 = reinterpret_cast<float4*>(row + cs);
+            const float4* src4 = reinterpret_cast<const float4*>(seg);
+#pragma unroll
+            for (int i = 0; i < kSegFloats / 128; i++) {
+                const int vi = lane + 32 * i;
+                if (vi < nv) dst4[vi] = src4[vi];
+            }
+            __syncwarp();
+            for (int d = dstart + lane; d < dlo; d += 32) seg[emis[d] - cs] = CUDART_INF_F;
+            __syncwarp();
+        }
+        // tail scalars (at most 3 columns)
+        {
+            const int ntail = (int)(F - body_end);
+            if (ntail > 0) {
+                float v = CUDART_INF_F;
+                for (int d = dlo; d < Db; d++) {
+                    if (emis[d] - body_end == lane) v = Pr[d];
+                }
+                if (lane < ntail) row[body_end + lane] = v;
+            }
+        }
+    }
+}
+
+// Deterministic reduction of the per-frame sums into two scalars (single block).
+__global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i64 T, i64 B,
+                                              float* loss2) {
+    typedef cub::BlockReduce<double, 1024> Red;
+    __shared__ typename Red::TempStorage tmp;
+    double s_all = 0.0, s_first = 0.0;
+    const i64 n = T * B;
+    for (i64 i = threadIdx.x; i < n; i += 1024) {
+        float v = sums[i];
+        s_all += v;
+        if (i < B) s_first += v;
+    }
+    double r0 = Red(tmp).Sum(s_all);
+    __syncthreads();
+    double r1 = Red(tmp).Sum(s_first);
+    if (threadIdx.x == 0) {
+        loss2[0] = (float)r0;
+        loss2[1] = (float)r1;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct RunLayout {
+    size_t A, Bt, Gt, Gf, P, total;
+};
+
+RunLayout run_layout(const fbw_b200_summary& s) {
+    RunLayout L;
+    size_t    off  = 0;
+    auto      take = [&](size_t floats) {
+        size_t o = off;
+        off += ((floats > 0 ? floats : 1) * 4 + 255) & ~(size_t)255;
+        return o;
+    };
+    L.A     = take((size_t)s.state_floats);
+    L.Bt    = take((size_t)s.state_floats);
+    L.Gt    = take((size_t)s.tiled_floats);
+    L.Gf    = take((size_t)s.frame_floats);
+    L.P     = take((size_t)s.frame_floats);
+    L.total = off;
+    return L;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            n = 148;
+        }
+    }
+    return n;
+}
+
+#define CUDA_OK(expr)                            \
+    do {                                         \
+        if ((expr) != cudaSuccess) {             \
+            return FBW_B200_CUDA_ERROR;          \
+        }                                        \
+    } while (0)
+
+template <int RING>
+int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
+                 int edges_in_smem, cudaStream_t st) {
+    if (smem > 48 * 1024) {
+        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem));
+    }
+    k_sweep<RING><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    return FBW_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fbw_b200_abi_version(void) { return 1; }
+
+const char* fbw_b200_status_string(int status) {
+    switch (status) {
+        case FBW_B200_OK: return "ok";
+        case FBW_B200_BAD_ARGUMENT: return "bad argument (null pointer, non-positive dimension or misaligned buffer)";
+        case FBW_B200_WORKSPACE: return "workspace too small";
+        case FBW_B200_CUDA_ERROR: return "CUDA runtime error";
+        case FBW_B200_BAD_AUTOMATON: return "automaton rejected (index out of range, state shared by two sequences, or a sequence too large)";
+        case FBW_B200_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+
+size_t fbw_b200_plan_bytes(int64_t B, int64_t E, int64_t S) {
+    if (B <= 0 || S <= 0 || E < 0) return 0;
+    return plan_layout(B, E, S).total;
+}
+
+int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* start_end,
+                     const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E, int64_t S,
+                     void* plan, size_t plan_bytes, fbw_b200_stream_t stream) {
+    if (T <= 0 || B <= 0 || F <= 0 || S <= 0 || E < 0) return FBW_B200_BAD_ARGUMENT;
+    if (B > 0x7fffffff / 2 || E > 0x7fffffff - 1 || S > 0x7fffffff - 1 || T > 0x7fffffff)
+        return FBW_B200_BAD_ARGUMENT;
+    if (!plan || !start_end || !seq_lens || (E > 0 && (!edges || !weights)))
+        return FBW_B200_BAD_ARGUMENT;
+    if (((uintptr_t)plan & 255) != 0) return FBW_B200_BAD_ARGUMENT;
+    const PlanLayout L = plan_layout(B, E, S);
+    if (plan_bytes < L.total) return FBW_B200_WORKSPACE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    fbw_b200_summary* hdr = at<fbw_b200_summary>(plan, L.header);
+    CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(fbw_b200_summary), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.state_key), 0xff, 4 * (size_t)S, st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.scount), 0, 4 * (size_t)(B + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.ecount), 0, 4 * (size_t)(B + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_f), 0, 4 * (size_t)(S + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_b), 0, 4 * (size_t)(S + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.hs), 0, 4 * (size_t)(E + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.m_ptr), 0, 4 * (size_t)(E + 1), st));
+
+    const int TB = 256;
+    auto blocks = [&](i64 n) { return (unsigned)((n + TB - 1) / TB); };
+    void*  ctemp = at<char>(plan, L.cub_temp);
+    size_t cbytes = L.cub_temp_bytes;
+
+    k_mark<<<blocks(E + B), TB, 0, st>>>(edges, start_end, E, B, S, F, at<int>(plan, L.state_key),
+                                         at<int>(plan, L.scount), at<int>(plan, L.ecount), hdr);
+    k_off1<<<1, 1024, 0, st>>>(at<int>(plan, L.scount), at<int>(plan, L.ecount), seq_lens, (int)B,
+                               T, at<int>(plan, L.state_off), at<int>(plan, L.edge_off),
+                               at<int>(plan, L.seq_T));
+    // states ordered by owning sequence (stable: ascending state id inside a sequence)
+    k_statekeys<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.state_key), S, (int)B,
+                                          at<unsigned>(plan, L.skey), at<int>(plan, L.siota));
+    CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.skey),
+                                            at<unsigned>(plan, L.skey_out),
+                                            at<int>(plan, L.siota), at<int>(plan, L.sorted_state),
+                                            (int)S, 0, bits_for((unsigned long long)B), st));
+    k_packed<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.sorted_state), S, at<int>(plan, L.packed_of));
+    if (E > 0) {
+        k_edgekeys<<<blocks(E), TB, 0, st>>>(edges, E, F, at<int>(plan, L.packed_of),
+                                             at<unsigned>(plan, L.keyq), at<unsigned>(plan, L.keyf),
+                                             at<unsigned>(plan, L.keyb),
+                                             at<unsigned long long>(plan, L.key64),
+                                             at<int>(plan, L.eiota), at<int>(plan, L.rowcnt_f),
+                                             at<int>(plan, L.rowcnt_b), hdr);
+        const int sb = bits_for((unsigned long long)S);
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyq),
+                                                at<unsigned>(plan, L.key32_out),
+                                                at<int>(plan, L.eiota), at<int>(plan, L.qe), (int)E,
+                                                0, bits_for((unsigned long long)B), st));
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyf),
+                                                at<unsigned>(plan, L.key32_out),
+                                                at<int>(plan, L.eiota), at<int>(plan, L.fe), (int)E,
+                                                0, sb, st));
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyb),
+                                                at<unsigned>(plan, L.key32_out),
+                                                at<int>(plan, L.eiota), at<int>(plan, L.be), (int)E,
+                                                0, sb, st));
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(
+            ctemp, cbytes, at<unsigned long long>(plan, L.key64),
+            at<unsigned long long>(plan, L.key64_out), at<int>(plan, L.eiota), at<int>(plan, L.me),
+            (int)E, 0, bits_for((unsigned long long)B * (unsigned long long)F), st));
+        CUDA_OK(cub::DeviceScan::ExclusiveSum(ctemp, cbytes, at<int>(plan, L.rowcnt_f),
+                                              at<int>(plan, L.rowptr_f), (int)(S + 1), st));
+        CUDA_OK(cub::DeviceScan::ExclusiveSum(ctemp, cbytes, at<int>(plan, L.rowcnt_b),
+                                              at<int>(plan, L.rowptr_b), (int)(S + 1), st));
+        k_heads<<<blocks(E + 1), TB, 0, st>>>(at<unsigned long long>(plan, L.key64_out), E,
+                                              at<int>(plan, L.head));
+        CUDA_OK(cub::DeviceScan::ExclusiveSum(ctemp, cbytes, at<int>(plan, L.head),
+                                              at<int>(plan, L.hs), (int)(E + 1), st));
+        k_slots<<<blocks(E + 1), TB, 0, st>>>(at<unsigned long long>(plan, L.key64_out),
+                                              at<int>(plan, L.me), at<int>(plan, L.head),
+                                              at<int>(plan, L.hs), E, F,
+                                              at<int>(plan, L.slot_of_edge),
+                                              at<int>(plan, L.slot_emis), at<int>(plan, L.m_ptr),
+                                              hdr);
+    } else {
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowptr_f), 0, 4 * (size_t)(S + 1), st));
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowptr_b), 0, 4 * (size_t)(S + 1), st));
+    }
+    k_off2<<<1, 1024, 0, st>>>(at<int>(plan, L.state_off), at<int>(plan, L.edge_off),
+                               at<int>(plan, L.hs), at<int>(plan, L.seq_T), start_end,
+                               at<int>(plan, L.packed_of), (int)B, T, F, E, S,
+                               at<int>(plan, L.slot_off), at<int>(plan, L.start_l),
+                               at<int>(plan, L.end_l), at<i64>(plan, L.ta_off),
+                               at<i64>(plan, L.tg_off), at<i64>(plan, L.gf_off),
+                               at<i64>(plan, L.gu_off), at<i64>(plan, L.pu_off), hdr);
+    if (E > 0) {
+        k_records<<<blocks(E), TB, 0, st>>>(
+            edges, weights, E, at<int>(plan, L.packed_of), at<int>(plan, L.state_off),
+            at<int>(plan, L.slot_off), at<int>(plan, L.slot_of_edge), at<int>(plan, L.qe),
+            at<int>(plan, L.fe), at<int>(plan, L.be), at<int>(plan, L.me),
+            at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec), at<int4>(plan, L.q_rec),
+            at<int4>(plan, L.m_rec), hdr);
+    }
+    CUDA_OK(cudaGetLastError());
+    return FBW_B200_OK;
+}
+
+int fbw_b200_plan_summary(const void* plan, fbw_b200_summary* summary, fbw_b200_stream_t stream) {
+    if (!plan || !summary) return FBW_B200_BAD_ARGUMENT;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    CUDA_OK(cudaMemcpyAsync(summary, plan, sizeof(fbw_b200_summary), cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaStreamSynchronize(st));
+    return summary->error ? FBW_B200_BAD_AUTOMATON : FBW_B200_OK;
+}
+
+size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
+    if (!summary) return 0;
+    return run_layout(*summary).total;
+}
+
+int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                 float* sums, float* loss2, void* work, size_t work_bytes,
+                 fbw_b200_stream_t stream) {
+    if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
+    if (summary->error) return FBW_B200_BAD_AUTOMATON;
+    if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
+    const fbw_b200_summary& s = *summary;
+    const RunLayout  R = run_layout(s);
+    if (work_bytes < R.total) return FBW_B200_WORKSPACE;
+    const PlanLayout L = plan_layout(s.B, s.E, s.S);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    RunArgs a;
+    a.am = am; a.out = out; a.sums = sums; a.loss2 = loss2;
+    a.A  = at<float>(work, R.A);
+    a.Bt = at<float>(work, R.Bt);
+    a.Gt = at<float>(work, R.Gt);
+    a.Gf = at<float>(work, R.Gf);
+    a.P  = at<float>(work, R.P);
+    a.state_off = at<int>(plan, L.state_off);
+    a.edge_off  = at<int>(plan, L.edge_off);
+    a.slot_off  = at<int>(plan, L.slot_off);
+    a.seq_T     = at<int>(plan, L.seq_T);
+    a.start_l   = at<int>(plan, L.start_l);
+    a.end_l     = at<int>(plan, L.end_l);
+    a.ta_off = at<i64>(plan, L.ta_off);
+    a.tg_off = at<i64>(plan, L.tg_off);
+    a.gf_off = at<i64>(plan, L.gf_off);
+    a.gu_off = at<i64>(plan, L.gu_off);
+    a.pu_off = at<i64>(plan, L.pu_off);
+    a.rowptr_f = at<int>(plan, L.rowptr_f);
+    a.rowptr_b = at<int>(plan, L.rowptr_b);
+    a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
+    a.bwd_rec  = at<uint2>(plan, L.bwd_rec);
+    a.q_rec    = at<int4>(plan, L.q_rec);
+    a.m_rec    = at<int4>(plan, L.m_rec);
+    a.m_ptr     = at<int>(plan, L.m_ptr);
+    a.slot_emis = at<int>(plan, L.slot_emis);
+    a.T = s.T; a.B = s.B; a.F = s.F;
+    a.gather_units = s.gather_units;
+    a.post_units   = s.post_units;
+
+    const int sms = sm_count();
+    // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
+    CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
+
+    if (s.gather_units > 0) {
+        int grid = (int)(s.gather_units < (i64)sms * 6 ? s.gather_units : (i64)sms * 6);
+        k_gather<<<grid, 256, 0, st>>>(a);
+    }
+    if (s.max_len > 0) {
+        int smax  = (int)((s.max_states + 3) & ~3);
+        int dpmax = (int)((s.max_slots + 3) & ~3);
+        int nt    = (int)((s.max_states + 31) & ~31);
+        nt = nt < 64 ? 64 : (nt > 1024 ? 1024 : nt);
+        const size_t limit = 227 * 1024;
+        auto need = [&](int ring, int in_smem) {
+            return (size_t)4 * ring * dpmax + (size_t)8 * smax + (size_t)4 * ((smax + 2) & ~1) +
+                   (in_smem ? (size_t)8 * s.max_edges : 0) + 16;
+        };
+        int ring = 8, in_smem = 1;
+        while (ring > 0 && need(ring, 1) > limit) ring = ring == 8 ? 4 : (ring == 4 ? 2 : 0);
+        if (need(ring, 1) > limit) {
+            in_smem = 0;
+            ring    = 8;
+            while (ring > 0 && need(ring, 0) > limit) ring = ring == 8 ? 4 : (ring == 4 ? 2 : 0);
+            if (need(ring, 0) > limit) return FBW_B200_TOO_LARGE;
+        }
+        const size_t smem = need(ring, in_smem);
+        const int grid = (int)(2 * s.B);
+        int rc;
+        switch (ring) {
+            case 8: rc = launch_sweep<8>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
+            case 4: rc = launch_sweep<4>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
+            case 2: rc = launch_sweep<2>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
+            default: rc = launch_sweep<0>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
+        }
+        if (rc != FBW_B200_OK) return rc;
+    }
+    if (s.post_units > 0) {
+        i64 want = (s.post_units + 3) / 4;
+        int grid = (int)(want < (i64)sms * 16 ? want : (i64)sms * 16);
+        k_post<<<grid, 128, 0, st>>>(a);
+    }
+    {
+        i64 want = (s.T * s.B + 7) / 8;
+        int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
+        k_expand<<<grid, 256, 0, st>>>(a);
+    }
+    if (loss2) k_loss<<<1, 1024, 0, st>>>(sums, s.T, s.B, loss2);
+    CUDA_OK(cudaGetLastError());
+    return FBW_B200_OK;
+}
+
+}  // extern "C"

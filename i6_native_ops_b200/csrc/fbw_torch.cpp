@@ -1,0 +1,184 @@
+// fbw_torch.cpp -- torch extension `fbw_core`: the Python-visible op over the C ABI of
+// include/fbw_b200.h.  Mirrors the reference binding i6_native_ops/fbw/fbw_torch.cpp:15-40:
+// same module members (`fbw`, `DebugOptions`), same seven positional arguments, same input
+// checks (CUDA, contiguous, dtype -> RuntimeError), same two outputs.
+//
+// Differences that do not change results: scratch comes from torch's caching allocator instead
+// of cudaMalloc/cudaFree per call (fbw_op.cu:283-286, 384-389); work is enqueued on torch's current
+// stream of the inputs' device under a device guard (the reference uses the legacy default stream
+// and the current device, common/returnn_definitions.h:29); sizes are 64-bit.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <vector>
+
+#include "fbw_b200.h"
+
+namespace py = pybind11;
+
+// Same fields and defaults as the reference's DebugOptions (i6_native_ops/fbw/DebugOptions.h:4-9).
+struct DebugOptions {
+    bool     dump_alignment = false;
+    bool     dump_output    = false;
+    unsigned dump_every     = 40u;
+    float    pruning        = 10.f;
+};
+
+namespace {
+
+void check_input(const torch::Tensor& x, torch::ScalarType dtype, const char* name) {
+    TORCH_CHECK(x.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(x.is_contiguous(), name, " must be contiguous");
+    TORCH_CHECK(x.scalar_type() == dtype, name, " must have dtype ", dtype);
+}
+
+void check_status(int status, const fbw_b200_summary* s = nullptr) {
+    if (status == FBW_B200_OK) return;
+    if (status == FBW_B200_BAD_AUTOMATON && s) {
+        TORCH_CHECK(false, "fbw: ", fbw_b200_status_string(status), " (validation bits ", s->error,
+                    ")");
+    }
+    if (status == FBW_B200_CUDA_ERROR) {
+        TORCH_CHECK(false, "fbw: CUDA error: ", cudaGetErrorString(cudaGetLastError()));
+    }
+    TORCH_CHECK(false, "fbw: ", fbw_b200_status_string(status));
+}
+
+torch::Tensor byte_buffer(size_t bytes, const torch::Device& dev) {
+    return torch::empty({(int64_t)(bytes > 0 ? bytes : 1)},
+                        torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+}
+
+struct Prepared {
+    torch::Tensor    plan;
+    fbw_b200_summary summary;
+};
+
+Prepared prepare_impl(const torch::Tensor& edges, const torch::Tensor& weights,
+                      const torch::Tensor& start_end_states, const torch::Tensor& seq_lens,
+                      int64_t T, int64_t F, int64_t num_states) {
+    check_input(edges, torch::kInt32, "edges");
+    check_input(weights, torch::kFloat32, "weights");
+    check_input(start_end_states, torch::kInt32, "start_end_states");
+    check_input(seq_lens, torch::kInt32, "seq_lens");
+    TORCH_CHECK(edges.dim() == 2 && edges.size(0) == 4, "edges must have shape (4, E)");
+    const int64_t E = edges.size(1);
+    TORCH_CHECK(weights.dim() == 1 && weights.size(0) == E, "weights must have shape (E,)");
+    TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(0) == 2,
+                "start_end_states must have shape (2, B)");
+    const int64_t B = start_end_states.size(1);
+    TORCH_CHECK(seq_lens.dim() == 1 && seq_lens.size(0) == B, "seq_lens must have shape (B,)");
+    TORCH_CHECK(T > 0 && B > 0 && F > 0, "am_scores must be non-empty");
+    TORCH_CHECK(num_states > 0, "num_states must be positive");
+
+    auto   stream = at::cuda::getCurrentCUDAStream();
+    size_t pbytes = fbw_b200_plan_bytes(B, E, num_states);
+    Prepared p;
+    p.plan = byte_buffer(pbytes, edges.device());
+    check_status(fbw_b200_prepare(edges.data_ptr<int32_t>(), weights.data_ptr<float>(),
+                                  start_end_states.data_ptr<int32_t>(),
+                                  seq_lens.data_ptr<int32_t>(), T, B, F, E, num_states,
+                                  p.plan.data_ptr(), pbytes,
+                                  reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    int st = fbw_b200_plan_summary(p.plan.data_ptr(), &p.summary,
+                                   reinterpret_cast<fbw_b200_stream_t>(stream.stream()));
+    check_status(st, &p.summary);
+    return p;
+}
+
+std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_scores,
+                                    bool want_loss) {
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const fbw_b200_summary& s = p.summary;
+    torch::Tensor out  = torch::empty_like(am_scores);
+    torch::Tensor sums = torch::empty({s.T, s.B}, am_scores.options());
+    torch::Tensor loss2;
+    if (want_loss) loss2 = torch::empty({2}, am_scores.options());
+    size_t wbytes = fbw_b200_run_bytes(&s);
+    torch::Tensor work = byte_buffer(wbytes, am_scores.device());
+    check_status(fbw_b200_run(p.plan.data_ptr(), &s, am_scores.data_ptr<float>(),
+                              out.data_ptr<float>(), sums.data_ptr<float>(),
+                              want_loss ? loss2.data_ptr<float>() : nullptr, work.data_ptr(),
+                              wbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    if (want_loss) return {out, sums, loss2};
+    return {out, sums};
+}
+
+}  // namespace
+
+// The op.  Signature and meaning of the reference's fbw() (fbw_torch.cpp:15-29): am_scores (T,B,F)
+// f32 negative log scores, edges (4,E) i32, weights (E) f32, start_end_states (2,B) i32, seq_lens
+// (B) i32, num_states -> [out (T,B,F) negative log posteriors, sum_output (T,B)].
+std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
+                               torch::Tensor& weights, torch::Tensor& start_end_states,
+                               torch::Tensor& seq_lens, unsigned num_states,
+                               DebugOptions debug_options) {
+    check_input(am_scores, torch::kFloat32, "am_scores");
+    TORCH_CHECK(am_scores.dim() == 3, "am_scores must have shape (T, B, F)");
+    TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == am_scores.size(1),
+                "start_end_states must have shape (2, B) with B = am_scores.size(1)");
+    c10::cuda::CUDAGuard guard(am_scores.device());
+    (void)debug_options;  // text dumps (fbw_op.cu:155-224) are not produced
+    Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, am_scores.size(0),
+                              am_scores.size(2), (int64_t)num_states);
+    return run_impl(p, am_scores, false);
+}
+
+// Two-step form of the same op for callers that reuse one batch of automata with new scores:
+// fbw_prepare(...) -> opaque handle, fbw_run(handle, am_scores) -> [out, sum_output, loss2].
+// loss2 = [sum of sum_output, sum over sequences of sum_output[0]].
+struct PlanHandle {
+    Prepared p;
+    py::dict info() const {
+        py::dict d;
+        const fbw_b200_summary& s = p.summary;
+        d["T"] = s.T; d["B"] = s.B; d["F"] = s.F; d["E"] = s.E; d["S"] = s.S;
+        d["state_floats"] = s.state_floats; d["tiled_floats"] = s.tiled_floats;
+        d["frame_floats"] = s.frame_floats; d["num_slots"] = s.num_slots;
+        d["max_states"] = s.max_states; d["max_edges"] = s.max_edges;
+        d["max_slots"] = s.max_slots; d["max_len"] = s.max_len; d["sum_len"] = s.sum_len;
+        d["gather_units"] = s.gather_units; d["post_units"] = s.post_units;
+        d["plan_bytes"] = (int64_t)p.plan.numel();
+        d["run_bytes"] = (int64_t)fbw_b200_run_bytes(&s);
+        return d;
+    }
+};
+
+PlanHandle fbw_prepare(torch::Tensor& edges, torch::Tensor& weights,
+                       torch::Tensor& start_end_states, torch::Tensor& seq_lens, int64_t T,
+                       int64_t F, int64_t num_states) {
+    TORCH_CHECK(edges.is_cuda(), "edges must be a CUDA tensor");
+    c10::cuda::CUDAGuard guard(edges.device());
+    PlanHandle h;
+    h.p = prepare_impl(edges, weights, start_end_states, seq_lens, T, F, num_states);
+    return h;
+}
+
+std::vector<torch::Tensor> fbw_run(const PlanHandle& h, torch::Tensor& am_scores) {
+    check_input(am_scores, torch::kFloat32, "am_scores");
+    const fbw_b200_summary& s = h.p.summary;
+    TORCH_CHECK(am_scores.dim() == 3 && am_scores.size(0) == s.T && am_scores.size(1) == s.B &&
+                    am_scores.size(2) == s.F,
+                "am_scores must have the (T, B, F) the plan was prepared for");
+    TORCH_CHECK(am_scores.device() == h.p.plan.device(), "am_scores and plan on different devices");
+    c10::cuda::CUDAGuard guard(am_scores.device());
+    return run_impl(h.p, am_scores, true);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");
+    m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
+    m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
+    m.def("abi_version", []() { return fbw_b200_abi_version(); });
+
+    py::class_<DebugOptions>(m, "DebugOptions")
+        .def(py::init<>())
+        .def_readwrite("dump_alignment", &DebugOptions::dump_alignment)
+        .def_readwrite("dump_output", &DebugOptions::dump_output)
+        .def_readwrite("dump_every", &DebugOptions::dump_every)
+        .def_readwrite("pruning", &DebugOptions::pruning);
+
+    py::class_<PlanHandle>(m, "PlanHandle").def("info", &PlanHandle::info);
+}

@@ -1,0 +1,83 @@
+"""Full-sum forward-backward loss: same Python surface as the reference package
+``i6_native_ops.fbw`` (``i6_native_ops/fbw/__init__.py:27-68``): ``core`` (extension module with
+``fbw`` and ``DebugOptions``), ``FastBaumWelchLoss`` and ``fbw_loss``.
+
+The native extension is required: importing this module fails if it is not built
+(``python -m i6_native_ops_b200.build``); there is no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import importlib.util
+import os
+from typing import Tuple
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB = os.path.join(_PKG, "libfbw_b200.so")
+_EXT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build", "fbw_core.so")
+
+
+def _load_core():
+    if not (os.path.isfile(_LIB) and os.path.isfile(_EXT)):
+        raise ImportError(
+            "i6_native_ops_b200: native extension not built "
+            f"(missing {_LIB if not os.path.isfile(_LIB) else _EXT}); "
+            "run `python -m i6_native_ops_b200.build`"
+        )
+    # the extension links against libfbw_b200.so by soname; load it first so the loader finds it
+    ctypes.CDLL(_LIB, mode=ctypes.RTLD_GLOBAL)
+    spec = importlib.util.spec_from_file_location("fbw_core", _EXT)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+core = _load_core()
+
+
+class FastBaumWelchLoss(torch.autograd.Function):
+    """``FastBaumWelchLoss.apply(neg_log_probs (T,B,F), fsa, seq_lens) -> (T,B)`` per-frame sums.
+
+    Forward saves the (T,B,F) negative log posteriors; backward returns ``exp(-saved)`` as the
+    gradient with respect to ``neg_log_probs`` and, like the reference
+    (``i6_native_ops/fbw/__init__.py:41-44``), does not scale by the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, am_scores, fsa, seq_lens):
+        num_states, edge_tensor, weight_tensor, start_end_states = fsa
+        grad, loss = core.fbw(
+            am_scores, edge_tensor, weight_tensor, start_end_states, seq_lens, int(num_states),
+            core.DebugOptions(),
+        )
+        ctx.save_for_backward(grad)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        grad = ctx.saved_tensors[0].neg().exp()  # negative log posterior -> posterior
+        return grad, None, None
+
+
+def fbw_loss(
+    log_probs: torch.Tensor,
+    fsa: Tuple[int, torch.Tensor, torch.Tensor, torch.Tensor],
+    seq_lens: torch.Tensor,
+) -> torch.Tensor:
+    """Negative log likelihood of an emission model given one automaton per sequence.
+
+    :param log_probs: (B, T, F) float32 log probabilities (CUDA)
+    :param fsa: ``(num_states, edges (4,E) int32 rows from/to/emission/sequence,
+        weights (E,) float32, start_end_states (2,B) int32)``
+    :param seq_lens: (B,) int32 lengths
+    :return: (T, B) per-frame normalisers (each valid frame of a sequence holds that sequence's
+        negative log likelihood; frames past its length hold 0), as the reference returns
+        (``i6_native_ops/fbw/__init__.py:66-68``).  ``loss.sum().backward()`` leaves
+        ``-posterior`` in ``log_probs.grad``.
+    """
+    neg_log_probs = log_probs.neg().transpose(0, 1).contiguous()  # (T, B, F)
+    return FastBaumWelchLoss.apply(neg_log_probs, fsa, seq_lens)
+
+
+__all__ = ["core", "FastBaumWelchLoss", "fbw_loss"]

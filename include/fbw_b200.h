@@ -1,0 +1,109 @@
+/* fbw_b200.h -- C ABI of the B200 (sm_100a) full-sum forward-backward ("fast Baum-Welch") op.
+ *
+ * This is the boundary a host binding links against.  Together the calls below replace the
+ * reference's host launcher  fbw_cuda()  (i6_native_ops/fbw/fbw_op.cu:226-393), which its
+ * binding  fbw()  (i6_native_ops/fbw/fbw_torch.cpp:15-29) calls with the same five arrays.
+ *
+ * All pointers are DEVICE pointers unless a comment says host.  Sizes are 64-bit.  No call
+ * allocates device memory; scratch is passed in by the caller.  Calls enqueue work on the given
+ * stream and return without synchronising, except fbw_b200_plan_summary.
+ *
+ * Call order for one op call:
+ *     plan  = caller-allocated  fbw_b200_plan_bytes(B, E, S)  bytes
+ *     fbw_b200_prepare(...)                      -- validates the automata, builds sorted edge lists
+ *     fbw_b200_plan_summary(plan, &sum, stream)  -- host gets sizes + validation result (synchronises)
+ *     work  = caller-allocated  fbw_b200_run_bytes(&sum)  bytes
+ *     fbw_b200_run(...)                          -- scores -> out, sums (and optional loss scalars)
+ * A plan depends only on the automata and seq_lens; it can be kept and reused with new scores.
+ */
+#ifndef FBW_B200_H
+#define FBW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* CUDA stream handle (cudaStream_t / CUstream) without pulling in CUDA headers. */
+typedef struct CUstream_st* fbw_b200_stream_t;
+
+/* Status codes (0 = success).  fbw_b200_status_string() gives the text.  The reference reports
+ * the same classes of failure as TORCH_CHECK errors / asserts
+ * (i6_native_ops/common/returnn_definitions.h:82-123). */
+enum {
+    FBW_B200_OK             = 0,
+    FBW_B200_BAD_ARGUMENT   = 1, /* null pointer, non-positive dimension, misaligned buffer      */
+    FBW_B200_WORKSPACE      = 2, /* caller-provided scratch too small                            */
+    FBW_B200_CUDA_ERROR     = 3, /* a CUDA runtime call failed (see cudaGetLastError)            */
+    FBW_B200_BAD_AUTOMATON  = 4, /* summary.error != 0: an index in edges/start_end out of range,
+                                    a state used by two sequences, or a per-sequence size limit */
+    FBW_B200_TOO_LARGE      = 5  /* request exceeds the fixed capacity of a no-allocation entry  */
+};
+
+/* Bits of fbw_b200_summary.error (validation of the automata; the reference does not validate,
+ * out-of-range input is undefined behaviour there). */
+enum {
+    FBW_B200_ERR_STATE_RANGE    = 1,  /* from/to state id outside [0, S)                  */
+    FBW_B200_ERR_EMISSION_RANGE = 2,  /* emission id outside [0, F)                       */
+    FBW_B200_ERR_SEQ_RANGE      = 4,  /* sequence id outside [0, B)                       */
+    FBW_B200_ERR_START_END      = 8,  /* start or end state outside [0, S)                */
+    FBW_B200_ERR_SHARED_STATE   = 16, /* one state id used by edges of two sequences      */
+    FBW_B200_ERR_SEQ_TOO_LARGE  = 32  /* a sequence has more than 65535 states or classes */
+};
+
+/* Sizes the host needs after fbw_b200_prepare (HOST struct). */
+typedef struct fbw_b200_summary {
+    int64_t error;        /* validation bits above; 0 = automata accepted                         */
+    int64_t T, B, F, E, S;
+    int64_t state_floats; /* floats in each of the two per-frame state-score arrays (alpha, beta) */
+    int64_t tiled_floats; /* floats in the tiled gathered-score array                              */
+    int64_t frame_floats; /* floats in each frame-major array (gathered scores, class posteriors) */
+    int64_t num_slots;    /* sum over sequences of distinct emission classes                      */
+    int64_t max_states, max_edges, max_slots, max_len; /* per-sequence maxima                    */
+    int64_t sum_len;      /* sum over sequences of valid frames                                   */
+    int64_t gather_units, post_units; /* work items of the gather / posterior kernels             */
+    int64_t reserved[4];
+} fbw_b200_summary;
+
+/* Bytes of plan scratch for B sequences, E edges, S states. */
+size_t fbw_b200_plan_bytes(int64_t B, int64_t E, int64_t S);
+
+/* Validate the automata and build the per-sequence sorted edge lists into `plan`.
+ * edges (4,E) int32 rows from/to/emission/sequence, weights (E) f32, start_end (2,B) int32,
+ * seq_lens (B) int32 -- the layouts of fbw_op.cu:249-263.  T,B,F are the dims of the score tensor.
+ * Replaces nothing in the reference one-to-one: the reference walks the unsorted edge list with
+ * atomics every frame (next_frame, fbw_op.cu:71-102); sorting once removes the atomics. */
+int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* start_end,
+                     const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E, int64_t S,
+                     void* plan, size_t plan_bytes, fbw_b200_stream_t stream);
+
+/* Copy the plan's summary to host memory.  SYNCHRONISES the stream.  Returns
+ * FBW_B200_BAD_AUTOMATON if validation failed (summary->error says why). */
+int fbw_b200_plan_summary(const void* plan, fbw_b200_summary* summary, fbw_b200_stream_t stream);
+
+/* Bytes of run scratch for a prepared plan. */
+size_t fbw_b200_run_bytes(const fbw_b200_summary* summary);
+
+/* The op: am (T,B,F) f32 negative log scores -> out (T,B,F) f32 negative log class posteriors
+ * (+inf where zero and for frames t >= seq_len) and sums (T,B) f32 per-frame normalisers
+ * (0 for t >= seq_len or when no path exists): the two tensors fbw_cuda returns
+ * (fbw_op.cu:230-232, 392).  Covers the alpha/beta initialisation (fbw_op.cu:297-302, 61-69),
+ * both sweeps (318-353), the normaliser (104-135) and the scatter into the output (137-153,
+ * 366-378).  loss2 (2 floats, may be NULL): [0] = sum of all sums, [1] = sum over sequences of
+ * sums[0,b]; written by the last kernel so a collective can follow on the same stream. */
+int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                 float* sums, float* loss2, void* work, size_t work_bytes,
+                 fbw_b200_stream_t stream);
+
+/* Text for a status code (static storage). */
+const char* fbw_b200_status_string(int status);
+
+/* ABI version of this header. */
+int fbw_b200_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBW_B200_H */

