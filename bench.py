@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Benchmark of the fbw (fast Baum-Welch) hot path.
+
+  python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload triphone]
+
+One step = one op call (automaton preparation + gather + both sweeps + posteriors + output) on
+one batch of synthetic input.  Default workload: the triphone configuration (B=64 sequences per
+GPU, T=1500, F=12001, fp32), the one the headline target is quoted on.  With N GPUs every rank
+owns 64 sequences of a 64*N batch (length-balanced partition by sequence, no data-path
+collective; one all-reduce of two loss scalars per step), i.e. weak scaling.
+
+Printed by rank 0: ONE JSON line.
+  value      frames/s (T*B per call, summed over ranks) with inputs resident in HBM
+  e2e        the same through the op with HOST buffers: pinned host -> device copy of the scores
+             and automata, the op, device -> host copy of the (T,B) result, all inside the timing
+  roofline   whole-call algorithmic bytes / measured call time against the measured HBM peak
+  cpu_baseline  the CPU oracle (a C/OpenMP port of the reference's arithmetic; the reference has no
+             CPU implementation of fbw) on a bounded sample of the same workload
+
+--impl reference times that CPU port alone (the reference's op is CUDA-only and has no CPU path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SEQS_PER_GPU = {"triphone": 64, "bpe_ctc": 256, "monophone": 32, "ctc_tiny": 4, "lattice": 64}
+CPU_SAMPLE_SEQS = None  # None: the full per-GPU batch of the workload
+
+# dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one triphone call divided by the
+# call's algorithmic bytes, from the ncu capture summarised in profiles/ (None until measured)
+TRAFFIC_PER_ALGORITHMIC_BYTE = None
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline_pass(workload: str, threads: int, passes: int, warm: int = 1):
+    """Times the CPU oracle (test infrastructure; the only use of oracle/ in this file) on a
+    bounded sample: one per-GPU batch of the workload at full T and F, a few passes."""
+    import oracle
+    from i6_native_ops_b200 import workloads as wl
+
+    batch = wl.make_batch(workload, B=CPU_SAMPLE_SEQS or SEQS_PER_GPU[workload])
+    am = wl.make_scores(batch, "cpu").numpy()
+    times = []
+    for i in range(warm + passes):
+        t0 = time.perf_counter()
+        oracle.fbw_oracle(am, batch.edges, batch.weights, batch.start_end, batch.seq_lens,
+                          batch.num_states, "f32", nthreads=threads)
+        dt = time.perf_counter() - t0
+        if i >= warm:
+            times.append(dt)
+    frames = batch.T * batch.B
+    sample = (f"{batch.B} sequences of {workload} at full T={batch.T}, F={batch.F}; fp32 CPU port of the "
+              f"reference arithmetic, OpenMP over sequences, {passes} passes")
+    return frames, times, sample
+
+
+def run_reference_arm(args):
+    """The reference arm: the reference's fbw has no CPU implementation (its binding rejects CPU
+    tensors), so this times the C/OpenMP port of its arithmetic on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    frames, times, sample = cpu_baseline_pass(args.workload, threads, args.steps, max(1, min(args.warmup, 2)))
+    total = float(sum(times))
+    value = frames * len(times) / total
+    line = {
+        "impl": "reference", "metric": "fbw fwd+bwd frames/s", "value": value, "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="new", choices=["new", "reference"])
+    ap.add_argument("--workload", default="triphone", choices=sorted(SEQS_PER_GPU))
+    ap.add_argument("--seqs-per-gpu", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from i6_native_ops_b200 import sharding
+    from i6_native_ops_b200 import workloads as wl
+    from i6_native_ops_b200.fbw import core
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- workload: 64*N sequences, partitioned by sequence, each rank builds its own shard ----
+    per_gpu = args.seqs_per_gpu or SEQS_PER_GPU[args.workload]
+    global_b = per_gpu * world
+    if world > 1:
+        full = wl.make_batch(args.workload, B=global_b)
+        costs = sharding.sequence_costs(full.states_per_seq, full.edges_per_seq, full.seq_lens,
+                                        full.T, full.F)
+        mine = sharding.partition(costs, world)[rank]
+        batch = wl.make_batch(args.workload, seq_ids=mine, T=full.T)
+    else:
+        batch = wl.make_batch(args.workload, B=global_b)
+    am = wl.make_scores(batch, dev)
+    fsa, seq_lens = wl.to_torch(batch, dev)
+    frames = batch.T * batch.B
+    alg_bytes = batch.algorithmic_bytes()
+
+    def step():
+        out, sums, loss2, _ = sharding.sharded_fbw(am, fsa, seq_lens, plan=None)
+        return sums, loss2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = core.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            sums, loss2 = step()
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = core.launch_count() - launches0
+    t_ms = torch.tensor([ms], device=dev, dtype=torch.float64)
+    tot = torch.tensor([float(frames), float(alg_bytes)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    ms = float(t_ms.item())
+    ms_per_step = ms / args.steps
+    total_frames, total_bytes = float(tot[0].item()), float(tot[1].item())
+    value = total_frames / (ms_per_step * 1e-3)
+
+    # ---- per-kernel device times of one call on this rank (outside the timed region) ----
+    plan = core.fbw_prepare(fsa[1], fsa[2], fsa[3], seq_lens, batch.T, batch.F, fsa[0])
+    phase = np.zeros(5)
+    reps = 5
+    for _ in range(reps):
+        _, times = core.fbw_run_phases(plan, am)
+        phase += np.array(times)
+    phase /= reps
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pe0.record()
+    for _ in range(reps):
+        core.fbw_prepare(fsa[1], fsa[2], fsa[3], seq_lens, batch.T, batch.F, fsa[0])
+    pe1.record()
+    torch.cuda.synchronize()
+    prep_ms = pe0.elapsed_time(pe1) / reps
+    del plan
+
+    # ---- end to end through the op with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
+        am_h.copy_(am)
+        host_fsa = [t.cpu().pin_memory() for t in (fsa[1], fsa[2], fsa[3], seq_lens)]
+        sums_h = torch.empty((batch.T, batch.B), dtype=torch.float32, pin_memory=True)
+        am_d = torch.empty_like(am)
+        del am
+        h2d = am_h.numel() * 4 + sum(t.numel() * t.element_size() for t in host_fsa)
+        d2h = sums_h.numel() * 4 + 8
+
+        def e2e_step():
+            am_d.copy_(am_h, non_blocking=True)
+            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
+            out, sums, loss2, _ = sharding.sharded_fbw(am_d, (fsa[0], e_, w_, se_), sl_, plan=None)
+            sums_h.copy_(sums, non_blocking=True)
+            return loss2.cpu()  # device -> host read of the reduced loss; synchronises
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        ev0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        ev1.record()
+        barrier()
+        t_e = torch.tensor([ev0.elapsed_time(ev1) / n_e2e], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+        e2e = {"value": total_frames / (float(t_e.item()) * 1e-3), "unit": "frames/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": float(t_e.item()), "steps": n_e2e}
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9  # this rank's call; ranks are symmetric
+        traffic = (None if TRAFFIC_PER_ALGORITHMIC_BYTE is None
+                   else float(TRAFFIC_PER_ALGORITHMIC_BYTE * alg_bytes))
+        line = {
+            "metric": "fbw fwd+bwd frames/s", "value": value, "unit": "frames/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "T": batch.T, "B_per_gpu": batch.B,
+                       "B_global": global_b, "F": batch.F, "edges_per_gpu": batch.num_edges,
+                       "states_per_gpu": batch.num_states, "partition": "by sequence, length-balanced",
+                       "l2": "inputs (4.6 GB scores per call) far exceed the 126 MB L2; no flush",
+                       "step": "prepare + run per call (automata re-sorted every step)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_call": int(alg_bytes),
+                         "scope": "whole op call (all kernels), per GPU"},
+            "kernels_ms": {"prepare": prep_ms, "gather": float(phase[0]), "sweep": float(phase[1]),
+                           "posterior": float(phase[2]), "expand": float(phase[3]),
+                           "loss": float(phase[4])},
+            "gpu_launches": int(launches),
+            "clocks": clk.summary(),
+            "e2e": e2e,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            cframes, ctimes, sample = cpu_baseline_pass(args.workload, threads, 5)
+            line["cpu_baseline"] = {"value": cframes * len(ctimes) / float(sum(ctimes)),
+                                    "unit": "frames/s", "cores": threads, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

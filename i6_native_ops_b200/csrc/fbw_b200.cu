@@ -33,6 +33,7 @@
 
 #include <cub/cub.cuh>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 
@@ -827,6 +828,9 @@ int sm_count() {
     return n;
 }
 
+std::atomic<long long> g_launches{0};
+#define COUNT_LAUNCH(n) g_launches.fetch_add((n), std::memory_order_relaxed)
+
 #define CUDA_OK(expr)                            \
     do {                                         \
         if ((expr) != cudaSuccess) {             \
@@ -842,6 +846,7 @@ int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int 
                                      (int)smem));
     }
     k_sweep<RING><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    COUNT_LAUNCH(1);
     return FBW_B200_OK;
 }
 
@@ -896,6 +901,7 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
     void*  ctemp = at<char>(plan, L.cub_temp);
     size_t cbytes = L.cub_temp_bytes;
 
+    COUNT_LAUNCH(E > 0 ? 9 : 5);  // k_mark, k_off1, k_statekeys, k_packed, k_off2 (+4 edge kernels)
     k_mark<<<blocks(E + B), TB, 0, st>>>(edges, start_end, E, B, S, F, at<int>(plan, L.state_key),
                                          at<int>(plan, L.scount), at<int>(plan, L.ecount), hdr);
     k_off1<<<1, 1024, 0, st>>>(at<int>(plan, L.scount), at<int>(plan, L.ecount), seq_lens, (int)B,
@@ -983,9 +989,9 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
     return run_layout(*summary).total;
 }
 
-int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
-                 float* sums, float* loss2, void* work, size_t work_bytes,
-                 fbw_b200_stream_t stream) {
+static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                    float* sums, float* loss2, void* work, size_t work_bytes,
+                    fbw_b200_stream_t stream, cudaEvent_t* ev) {
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -1029,10 +1035,13 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
 
+    if (ev) CUDA_OK(cudaEventRecord(ev[0], st));
     if (s.gather_units > 0) {
         int grid = (int)(s.gather_units < (i64)sms * 6 ? s.gather_units : (i64)sms * 6);
         k_gather<<<grid, 256, 0, st>>>(a);
+        COUNT_LAUNCH(1);
     }
+    if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
     if (s.max_len > 0) {
         int smax  = (int)((s.max_states + 3) & ~3);
         int dpmax = (int)((s.max_slots + 3) & ~3);
@@ -1062,19 +1071,56 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
         }
         if (rc != FBW_B200_OK) return rc;
     }
+    if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
     if (s.post_units > 0) {
         i64 want = (s.post_units + 3) / 4;
         int grid = (int)(want < (i64)sms * 16 ? want : (i64)sms * 16);
         k_post<<<grid, 128, 0, st>>>(a);
+        COUNT_LAUNCH(1);
     }
+    if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
     {
         i64 want = (s.T * s.B + 7) / 8;
         int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
         k_expand<<<grid, 256, 0, st>>>(a);
+        COUNT_LAUNCH(1);
     }
-    if (loss2) k_loss<<<1, 1024, 0, st>>>(sums, s.T, s.B, loss2);
+    if (ev) CUDA_OK(cudaEventRecord(ev[4], st));
+    if (loss2) {
+        k_loss<<<1, 1024, 0, st>>>(sums, s.T, s.B, loss2);
+        COUNT_LAUNCH(1);
+    }
+    if (ev) CUDA_OK(cudaEventRecord(ev[5], st));
     CUDA_OK(cudaGetLastError());
     return FBW_B200_OK;
 }
+
+int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                 float* sums, float* loss2, void* work, size_t work_bytes,
+                 fbw_b200_stream_t stream) {
+    return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr);
+}
+
+int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,
+                        float* out, float* sums, float* loss2, void* work, size_t work_bytes,
+                        fbw_b200_stream_t stream, float* phase_ms) {
+    if (!phase_ms) return FBW_B200_BAD_ARGUMENT;
+    cudaEvent_t ev[FBW_B200_NUM_PHASES + 1];
+    for (int i = 0; i <= FBW_B200_NUM_PHASES; i++) CUDA_OK(cudaEventCreate(&ev[i]));
+    int rc = run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, ev);
+    if (rc == FBW_B200_OK) {
+        if (cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+            rc = FBW_B200_CUDA_ERROR;
+        }
+    }
+    for (int i = 0; i < FBW_B200_NUM_PHASES; i++) {
+        phase_ms[i] = 0.f;
+        if (rc == FBW_B200_OK) cudaEventElapsedTime(&phase_ms[i], ev[i], ev[i + 1]);
+    }
+    for (int i = 0; i <= FBW_B200_NUM_PHASES; i++) cudaEventDestroy(ev[i]);
+    return rc;
+}
+
+int64_t fbw_b200_launch_count(void) { return (int64_t)g_launches.load(); }
 
 }  // extern "C"

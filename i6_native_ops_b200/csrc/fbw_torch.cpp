@@ -18,13 +18,18 @@
 
 namespace py = pybind11;
 
+namespace fbw_b200 {
 // Same fields and defaults as the reference's DebugOptions (i6_native_ops/fbw/DebugOptions.h:4-9).
+// Lives in its own namespace and is registered module-local so that this module and the
+// reference's can be imported into one process.
 struct DebugOptions {
     bool     dump_alignment = false;
     bool     dump_output    = false;
     unsigned dump_every     = 40u;
     float    pruning        = 10.f;
 };
+}  // namespace fbw_b200
+using fbw_b200::DebugOptions;
 
 namespace {
 
@@ -167,18 +172,46 @@ std::vector<torch::Tensor> fbw_run(const PlanHandle& h, torch::Tensor& am_scores
     return run_impl(h.p, am_scores, true);
 }
 
+// fbw_run with per-kernel device times: returns ([out, sum_output, loss2], [ms per phase]).
+py::tuple fbw_run_phases(const PlanHandle& h, torch::Tensor& am_scores) {
+    check_input(am_scores, torch::kFloat32, "am_scores");
+    const fbw_b200_summary& s = h.p.summary;
+    TORCH_CHECK(am_scores.dim() == 3 && am_scores.size(0) == s.T && am_scores.size(1) == s.B &&
+                    am_scores.size(2) == s.F,
+                "am_scores must have the (T, B, F) the plan was prepared for");
+    c10::cuda::CUDAGuard guard(am_scores.device());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    torch::Tensor out   = torch::empty_like(am_scores);
+    torch::Tensor sums  = torch::empty({s.T, s.B}, am_scores.options());
+    torch::Tensor loss2 = torch::empty({2}, am_scores.options());
+    size_t wbytes = fbw_b200_run_bytes(&s);
+    torch::Tensor work = byte_buffer(wbytes, am_scores.device());
+    float ms[FBW_B200_NUM_PHASES];
+    check_status(fbw_b200_run_phases(h.p.plan.data_ptr(), &s, am_scores.data_ptr<float>(),
+                                     out.data_ptr<float>(), sums.data_ptr<float>(),
+                                     loss2.data_ptr<float>(), work.data_ptr(), wbytes,
+                                     reinterpret_cast<fbw_b200_stream_t>(stream.stream()), ms));
+    py::list times;
+    for (int i = 0; i < FBW_B200_NUM_PHASES; i++) times.append(ms[i]);
+    py::list outs;
+    outs.append(out); outs.append(sums); outs.append(loss2);
+    return py::make_tuple(outs, times);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("fbw_run_phases", &fbw_run_phases, "fbw_run with per-kernel device times");
+    m.def("launch_count", []() { return fbw_b200_launch_count(); });
     m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");
     m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
     m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
     m.def("abi_version", []() { return fbw_b200_abi_version(); });
 
-    py::class_<DebugOptions>(m, "DebugOptions")
+    py::class_<DebugOptions>(m, "DebugOptions", py::module_local())
         .def(py::init<>())
         .def_readwrite("dump_alignment", &DebugOptions::dump_alignment)
         .def_readwrite("dump_output", &DebugOptions::dump_output)
         .def_readwrite("dump_every", &DebugOptions::dump_every)
         .def_readwrite("pruning", &DebugOptions::pruning);
 
-    py::class_<PlanHandle>(m, "PlanHandle").def("info", &PlanHandle::info);
+    py::class_<PlanHandle>(m, "PlanHandle", py::module_local()).def("info", &PlanHandle::info);
 }

@@ -97,6 +97,20 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
                  float* sums, float* loss2, void* work, size_t work_bytes,
                  fbw_b200_stream_t stream);
 
+/* fbw_b200_run with per-phase device timing, for benchmarks and profiles: same arguments and
+ * results, plus phase_ms (HOST, FBW_B200_NUM_PHASES floats) = milliseconds of the gather, sweep,
+ * posterior, expand and loss-reduction kernels measured with CUDA events on `stream`.
+ * SYNCHRONISES the stream and creates/destroys events; not for production use.  No counterpart in
+ * the reference (it has no timing code in fbw). */
+#define FBW_B200_NUM_PHASES 5
+int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,
+                        float* out, float* sums, float* loss2, void* work, size_t work_bytes,
+                        fbw_b200_stream_t stream, float* phase_ms);
+
+/* Number of kernels of this library launched by this process so far (its own kernels only, not
+ * the CUB sort/scan kernels it calls during prepare).  No counterpart in the reference. */
+int64_t fbw_b200_launch_count(void);
+
 /* Text for a status code (static storage). */
 const char* fbw_b200_status_string(int status);
 
