@@ -52,36 +52,48 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi.  start() launches the
+    sampler and waits for its first line (nvidia-smi's start-up stalls CUDA calls for a while, so
+    it has to be over before anything is timed); window() marks the timed region; summary()
+    reports the samples that fell inside it (or the nearest ones if the region was shorter than
+    one sampling period)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_ms: int = 25):
         self.index = index
+        self.period_ms = period_ms
         self.proc = None
-        self.lines = []
+        self.lines = []  # (arrival time, text)
+        self.t0 = self.t1 = None
 
-    def __enter__(self):
+    def start(self, timeout: float = 20.0):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
         except OSError:
             self.proc = None
+            return self
+        threading.Thread(target=self._read, daemon=True).start()
+        end = time.time() + timeout
+        while not self.lines and time.time() < end:
+            time.sleep(0.05)
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def __exit__(self, *exc):
+    def window(self, t0: float, t1: float):
+        self.t0, self.t1 = t0, t1
+
+    def stop(self):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(2.5 * self.period_ms / 1000.0)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
@@ -89,24 +101,27 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        rows = []
+        for ts, ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 6:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                rows.append((ts, float(parts[0]), float(parts[1]),
+                             [n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)),
-                "reasons": sorted(reasons), "samples": len(sm)}
+        pad = self.period_ms / 1000.0
+        inside = [r for r in rows if self.t0 is not None and self.t0 <= r[0] <= self.t1 + pad]
+        if not inside and self.t0 is not None:  # region shorter than a period: nearest sample
+            inside = [min(rows, key=lambda r: abs(r[0] - self.t1))]
+        use = inside or rows
+        reasons = sorted({n for r in use for n in r[3]})
+        return {"sm_mhz": float(np.median([r[1] for r in use])), "sm_max_mhz": float(max(r[2] for r in use)),
+                "reasons": reasons, "samples": len(use)}
 
 
 def cpu_baseline_pass(workload: str, threads: int, passes: int, warm: int = 1):
@@ -215,18 +230,21 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    clk = ClockSampler(local_rank).start()
     for _ in range(args.warmup):
         step()
     barrier()
     launches0 = core.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clk:
-        barrier()
-        ev0.record()
-        for _ in range(args.steps):
-            sums, loss2 = step()
-        ev1.record()
-        barrier()
+    barrier()
+    w0 = time.time()
+    ev0.record()
+    for _ in range(args.steps):
+        sums, loss2 = step()
+    ev1.record()
+    barrier()
+    clk.window(w0, time.time())
+    clk.stop()
     ms = ev0.elapsed_time(ev1)
     launches = core.launch_count() - launches0
     t_ms = torch.tensor([ms], device=dev, dtype=torch.float64)

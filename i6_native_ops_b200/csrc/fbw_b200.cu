@@ -170,6 +170,29 @@ __device__ __forceinline__ float prob_add(float a, float b) {
     return -log1pf(expf(-fabsf(diff))) + fminf(a, b);
 }
 
+// prob_add with an exact shortcut.  prob_add(a,b) = fl(m - L), m = min(a,b), L = log1pf(expf(-d)),
+// d = |a-b|.  L <= 2^(-d*log2(e)) (1 + 2^-20); if that is below a quarter of the smallest gap between
+// m and a neighbouring float (2^(e-24) with e the exponent of m, taken at a power of two), the sum
+// rounds back to m, so  d*log2(e) > 27 - e  implies the result is m bit for bit.  A NaN difference
+// fails the test and takes the full path.
+__device__ __forceinline__ bool prob_add_is_min(float a, float b, float m) {
+    const float d = fabsf(a - b);
+    const int   e = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
+    return d * 1.442695f > (float)(27 - e);
+}
+
+// first term of an accumulation that starts at +inf: prob_add(+inf, y) is y (or +inf for NaN)
+__device__ __forceinline__ float prob_first(float y) { return isnan(y) ? CUDART_INF_F : y; }
+
+// prob_add(acc, x) through the exact shortcuts: +inf terms, a first term, a provably dominated term
+__device__ __forceinline__ float prob_add_fast(float acc, float x) {
+    if (x == CUDART_INF_F) return acc;
+    if (acc == CUDART_INF_F) return prob_first(x);
+    const float m = fminf(acc, x);
+    if (prob_add_is_min(acc, x, m)) return m;
+    return prob_add(acc, x);
+}
+
 // largest b in [0,B) with off[b] <= u, given off[0] <= u < off[B]
 __device__ __forceinline__ int find_seq(const i64* __restrict__ off, int B, i64 u) {
     int lo = 0, hi = B;
@@ -525,16 +548,20 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
     }
 }
 
+constexpr int kRegEdges = 4;  // in-edges (out-edges backward) of a thread's state kept in registers
+
 // One persistent CTA per (sequence, direction).  Shared memory holds the sequence's sorted edge list
-// (target-sorted for the forward sweep, source-sorted for the backward one), two state-score
+// (target-sorted for the forward sweep, source-sorted for the backward one), the state-score
 // vectors and a ring of RING gathered-score rows filled by cp.async a few frames ahead.
 // Forward: alpha_0 = {start: 0}; alpha_{t+1}(s) = fold over in-edges, ascending edge index, of
 // (alpha_t(from) + w) + score_t(emission).  alpha_t for t < len is stored (tiled) for k_post.
 // Backward: beta_len = {end: 0}; beta_t(s) = fold over out-edges of (beta_{t+1}(to) + w) + score_t;
 // the array stores beta_{t+1} at frame index t, which is what the edge score of frame t needs.
+// TILED: the state vectors of the last 64 frames stay in shared memory and each finished 32-frame
+// tile is written out as full 128-byte lines; otherwise every frame's vector is scattered out.
 // Replaces set_start_states / init_bwd_state_buffer / next_frame / fill_array and the two host loops
 // (fbw_op.cu:17-29, 61-102, 297-353).
-template <int RING>
+template <int RING, bool TILED>
 __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int item = blockIdx.x;
@@ -547,11 +574,13 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     const int Db = a.slot_off[b + 1] - a.slot_off[b];
     const int Dp = (Db + 3) & ~3;
     const int NT = blockDim.x, tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
+    constexpr int kRows = TILED ? 64 : 2;
+    const int spad = TILED ? (smax | 1) : smax;  // odd row stride: conflict-free transposed reads
 
-    float* ring = reinterpret_cast<float*>(smem_raw);                       // RING * dpmax
-    float* buf0 = ring + (size_t)(RING > 0 ? RING : 0) * dpmax;             // smax
-    float* buf1 = buf0 + smax;                                              // smax
-    int*   rp   = reinterpret_cast<int*>(buf1 + smax);                      // smax + 1 (+ pad)
+    float* ring  = reinterpret_cast<float*>(smem_raw);                      // RING * dpmax
+    float* sbase = ring + (size_t)RING * dpmax;                             // kRows * spad
+    int*   rp    = reinterpret_cast<int*>(sbase + (((size_t)kRows * spad + 3) & ~(size_t)3));
     uint2* recs_s = reinterpret_cast<uint2*>(rp + ((smax + 2) & ~1));
 
     const int* __restrict__ rowptr = (fwd ? a.rowptr_f : a.rowptr_b) + s0;
@@ -562,14 +591,42 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
         for (int i = tid; i < Eb; i += NT) recs_s[i] = recs_g[i];
         recs = recs_s;
     }
-    const int seed = fwd ? a.start_l[b] : a.end_l[b];
-    for (int s = tid; s < Sb; s += NT) buf0[s] = (s == seed) ? 0.f : CUDART_INF_F;
+    const int step = fwd ? 1 : -1;
+    const int t_first = fwd ? 0 : Te - 1;
+    auto srow = [&](int j, int t) -> float* {
+        return sbase + (size_t)(TILED ? (t & 63) : (j & 1)) * spad;
+    };
+    {
+        const int seed = fwd ? a.start_l[b] : a.end_l[b];
+        float* r0 = srow(0, t_first);
+        for (int s = tid; s < Sb; s += NT) r0[s] = (s == seed) ? 0.f : CUDART_INF_F;
+    }
+    __syncthreads();
+
+    // the first state of this thread: its edges live in registers
+    int   rfrom[kRegEdges], rslot[kRegEdges];
+    float rw[kRegEdges];
+    int   rcnt = 0, xi0 = 0, xi1 = 0;
+    if (tid < Sb) {
+        const int i0 = rp[tid], i1 = rp[tid + 1];
+        rcnt = min(i1 - i0, kRegEdges);
+        xi0  = i0 + rcnt;
+        xi1  = i1;
+#pragma unroll
+        for (int k = 0; k < kRegEdges; k++) {
+            const uint2 r = k < rcnt ? recs[i0 + k] : make_uint2(0u, 0u);
+            rfrom[k] = (int)(r.x & 0xffffu);
+            rslot[k] = (int)(r.x >> 16);
+            rw[k]    = __uint_as_float(r.y);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRegEdges; k++) { rfrom[k] = 0; rslot[k] = 0; rw[k] = 0.f; }
+    }
 
     const float* __restrict__ gf = a.Gf + a.gf_off[b];
     float* __restrict__ dst = (fwd ? a.A : a.Bt) + a.ta_off[b];
     const int nvec = Dp >> 2;
-    const int step = fwd ? 1 : -1;
-    const int t_first = fwd ? 0 : Te - 1;
     // frames whose scores are consumed: forward 0..Te-2, backward Te-1..1
     auto issue = [&](int j) {  // j-th consumed frame
         if (RING > 0) {
@@ -586,48 +643,90 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
 #pragma unroll
         for (int j = 0; j < RING - 1; j++) issue(j);
     }
+    // write frames lo..hi (all inside tile k) of the shared-memory ring out as [state][32] lines
+    auto flush_tile = [&](int k, int lo, int hi) {
+        const int  frame = k * kTile + lane;
+        const bool in    = frame >= lo && frame <= hi;
+        const float* src = sbase + (size_t)(frame & 63) * spad;
+        float* d = dst + (i64)k * Sb * kTile + lane;
+        for (int s = warp; s < Sb; s += nwarps) {
+            if (in) d[(i64)s * kTile] = src[s];
+        }
+    };
 
     constexpr int kWait = RING > 1 ? RING - 2 : 0;
-    float* cur = buf0;
-    float* nxt = buf1;
     for (int j = 0; j < Te; j++) {
         const int t = t_first + step * j;
         if (RING > 0) cp_async_wait<kWait>();
         __syncthreads();
         if (RING > 0) issue(j + RING - 1);
-        // record this frame's state scores (tiled layout: [t/32][state][t%32])
-        float* drow = dst + ((i64)(t >> 5) * Sb) * kTile + (t & 31);
-        for (int s = tid; s < Sb; s += NT) drow[(i64)s * kTile] = cur[s];
-        if (j == Te - 1) break;
-        const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
-                                  : gf + (i64)t * Dp;
-        for (int s = tid; s < Sb; s += NT) {
-            float acc = CUDART_INF_F;
-            const int i1 = rp[s + 1];
-            for (int i = rp[s]; i < i1; i++) {
-                const uint2 r  = recs[i];
-                const float pv = cur[r.x & 0xffffu];
-                if (!isinf(pv)) {
-                    const float val = (pv + __uint_as_float(r.y)) + g[r.x >> 16];
-                    acc = prob_add(acc, val);
-                }
-            }
-            nxt[s] = acc;
+        const float* cur = srow(j, t);
+        if (!TILED) {  // record this frame's state scores (tiled layout: [t/32][state][t%32])
+            float* drow = dst + ((i64)(t >> 5) * Sb) * kTile + (t & 31);
+            for (int s = tid; s < Sb; s += NT) drow[(i64)s * kTile] = cur[s];
         }
-        float* tmp = cur;
-        cur = nxt;
-        nxt = tmp;
+        const bool last = j == Te - 1;
+        if (!last) {
+            float* nxt = srow(j + 1, t + step);
+            const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
+                                      : gf + (i64)t * Dp;
+            if (tid < Sb) {
+                float v[kRegEdges];
+#pragma unroll
+                for (int k = 0; k < kRegEdges; k++) {
+                    const float pv = cur[rfrom[k]];
+                    const float gg = g[rslot[k]];
+                    v[k] = (k < rcnt && !isinf(pv)) ? (pv + rw[k]) + gg : CUDART_INF_F;
+                }
+                float acc = CUDART_INF_F;
+#pragma unroll
+                for (int k = 0; k < kRegEdges; k++) acc = prob_add_fast(acc, v[k]);
+                for (int i = xi0; i < xi1; i++) {
+                    const uint2 r  = recs[i];
+                    const float pv = cur[r.x & 0xffffu];
+                    if (!isinf(pv)) {
+                        acc = prob_add_fast(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
+                    }
+                }
+                nxt[tid] = acc;
+            }
+            for (int s = tid + NT; s < Sb; s += NT) {
+                float acc = CUDART_INF_F;
+                const int i1 = rp[s + 1];
+                for (int i = rp[s]; i < i1; i++) {
+                    const uint2 r  = recs[i];
+                    const float pv = cur[r.x & 0xffffu];
+                    if (!isinf(pv)) {
+                        acc = prob_add_fast(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
+                    }
+                }
+                nxt[s] = acc;
+            }
+        }
+        if (TILED) {
+            const int k = t >> 5;
+            if (fwd) {
+                if ((t & 31) == 31 || last) flush_tile(k, k * kTile, t);
+            } else {
+                if ((t & 31) == 0) flush_tile(k, t, min(k * kTile + 31, Te - 1));
+            }
+        }
+        if (last) break;
     }
     if (RING > 0) cp_async_wait<0>();
 }
+
+constexpr int kPostChunk = 8;  // edges whose loads are in flight while the previous 8 are folded
 
 // Edge scores, normaliser and class posteriors; one warp per (sequence, 32-frame tile), lane = frame.
 // For frame t:  x_e = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)   (fbw_op.cu:93-100)
 //   sum  = left fold of prob_add over the sequence's edges in ascending edge index (fbw_op.cu:115-118)
 //   sums[t,b] = isinf(sum) ? 0 : sum                                              (fbw_op.cu:120-129)
 //   post[t][slot] = fold over the slot's edges of (x_e - sum)                     (fbw_op.cu:131-153)
-// prob_add(acc, +inf) == acc exactly, so dead edges are skipped without changing any bit.
-__global__ void __launch_bounds__(128) k_post(RunArgs a) {
+// The tiled layouts make every load of a warp one 128-byte line.  Loads of the next chunk of edges
+// are issued before the current chunk is folded, so the serial fold never waits on memory; steps
+// whose result is provably the running minimum in every lane skip expf/log1pf.
+__global__ void __launch_bounds__(128, 4) k_post(RunArgs a) {
     __shared__ float stage[4][kTile][kTile + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int B = (int)a.B;
@@ -642,49 +741,103 @@ __global__ void __launch_bounds__(128) k_post(RunArgs a) {
         const int Te = a.seq_T[b];
         const int t  = k * kTile + lane;
         const bool valid = t < Te;
+        // every lane loads (the tile is allocated for all 32 frames); lanes past the sequence's
+        // length read unspecified values and are forced to +inf below
         const float* __restrict__ Ab = a.A + a.ta_off[b] + (i64)k * Sb * kTile + lane;
         const float* __restrict__ Bb = a.Bt + a.ta_off[b] + (i64)k * Sb * kTile + lane;
         const float* __restrict__ Gb = a.Gt + a.tg_off[b] + (i64)k * Db * kTile + lane;
-        const int4* __restrict__ q = a.q_rec + e0;
 
-        auto edge_score = [&](const int4 r) -> float {
-            float al = valid ? Ab[(i64)r.x * kTile] : CUDART_INF_F;
-            float be = valid ? Bb[(i64)r.y * kTile] : CUDART_INF_F;
-            float g  = valid ? Gb[(i64)r.z * kTile] : CUDART_INF_F;
-            // the reference writes +inf for an edge whose source (forward) or target (backward)
-            // state is unreachable (fbw_op.cu:82-85) before any addition
-            if (isinf(al) || isinf(be)) return CUDART_INF_F;
-            return ((al + __int_as_float(r.w)) + g) + be;
+        // raw operands of a chunk of edges: straight-line loads, no control flow between them,
+        // so all of a chunk's loads are in flight together
+        struct Chunk {
+            float al[kPostChunk], be[kPostChunk], g[kPostChunk], w[kPostChunk];
+            int   sl[kPostChunk];
+        };
+        auto load_chunk = [&](const int4* __restrict__ recs, int i0, Chunk& c) {
+            int4 r[kPostChunk];
+#pragma unroll
+            for (int j = 0; j < kPostChunk; j++) {
+                r[j] = __ldg(recs + min(i0 + j, Eb - 1));
+            }
+#pragma unroll
+            for (int j = 0; j < kPostChunk; j++) {
+                c.al[j] = Ab[(i64)r[j].x * kTile];
+                c.be[j] = Bb[(i64)r[j].y * kTile];
+                c.g[j]  = Gb[(i64)r[j].z * kTile];
+                c.w[j]  = __int_as_float(r[j].w);
+                c.sl[j] = i0 + j < Eb ? r[j].z : -1;
+            }
+        };
+        // the reference writes +inf for an edge whose source (forward) or target (backward) state
+        // is unreachable (fbw_op.cu:82-85) before any addition
+        auto score = [&](const Chunk& c, int j) -> float {
+            const float x = ((c.al[j] + c.w[j]) + c.g[j]) + c.be[j];
+            const bool dead = !valid || c.sl[j] < 0 || isinf(c.al[j]) || isinf(c.be[j]);
+            return dead ? CUDART_INF_F : x;
         };
 
+        // ---- normaliser: serial left fold in ascending edge index -------------------------------
         float acc = CUDART_INF_F;
-        for (int i = 0; i < Eb; i++) {
-            const float x = edge_score(q[i]);
-            if (!(x == CUDART_INF_F)) acc = prob_add(acc, x);
+        if (Eb > 0) {
+            const int4* __restrict__ q = a.q_rec + e0;
+            Chunk nx;
+            load_chunk(q, 0, nx);
+            for (int i0 = 0; i0 < Eb; i0 += kPostChunk) {
+                float x[kPostChunk];
+#pragma unroll
+                for (int j = 0; j < kPostChunk; j++) x[j] = score(nx, j);
+                if (i0 + kPostChunk < Eb) load_chunk(q, i0 + kPostChunk, nx);
+#pragma unroll
+                for (int j = 0; j < kPostChunk; j++) acc = prob_add_fast(acc, x[j]);
+            }
         }
         if (valid) a.sums[(i64)t * B + b] = isinf(acc) ? 0.f : acc;
 
-        const int4* __restrict__ m  = a.m_rec;
-        const int* __restrict__ mp  = a.m_ptr + so;
-        float* __restrict__ Pb      = a.P + a.gf_off[b];
-        for (int d0 = 0; d0 < Db; d0 += kTile) {
-            const int nd = min(kTile, Db - d0);
-            for (int dd = 0; dd < nd; dd++) {
-                float p = CUDART_INF_F;
-                const int j1 = mp[d0 + dd + 1];
-                for (int j = mp[d0 + dd]; j < j1; j++) {
-                    const float x = edge_score(m[j]);
-                    p = prob_add(p, x - acc);
-                }
-                st[dd][lane] = p;
-            }
+        // ---- class posteriors: edges in (slot, edge index) order ---------------------------------
+        float* __restrict__ Pb = a.P + a.gf_off[b];
+        auto flush_block = [&](int d0, int nd) {  // slots d0..d0+nd-1 are staged: transpose out
             __syncwarp();
-            // transpose: row r of the tile gets its nd posteriors as one contiguous write
             for (int r = 0; r < kTile; r++) {
                 const int tr = k * kTile + r;
                 if (tr < Te && lane < nd) Pb[(i64)tr * Dp + d0 + lane] = st[lane][r];
             }
             __syncwarp();
+        };
+        if (Eb > 0) {
+            const int4* __restrict__ m = a.m_rec + e0;
+            Chunk nx;
+            load_chunk(m, 0, nx);
+            int   cur = -1;
+            float p   = CUDART_INF_F;
+            for (int i0 = 0; i0 < Eb; i0 += kPostChunk) {
+                float y[kPostChunk];
+                int   s[kPostChunk];
+#pragma unroll
+                for (int j = 0; j < kPostChunk; j++) {
+                    y[j] = score(nx, j) - acc;
+                    s[j] = nx.sl[j];
+                }
+                if (i0 + kPostChunk < Eb) load_chunk(m, i0 + kPostChunk, nx);
+#pragma unroll
+                for (int j = 0; j < kPostChunk; j++) {
+                    if (s[j] < 0) continue;  // past the end (uniform)
+                    if (s[j] != cur) {       // uniform: a new slot starts
+                        if (cur >= 0) {
+                            st[cur & 31][lane] = p;
+                            if ((cur & 31) == 31) flush_block(cur & ~31, 32);
+                        }
+                        cur = s[j];
+                        p   = prob_first(y[j]);
+                    } else {
+                        // prob_add(p, y) with the exact shortcuts; y may be NaN (inf - inf)
+                        p = (p == CUDART_INF_F) ? prob_first(y[j]) : prob_add_fast(p, y[j]);
+                    }
+                }
+            }
+            if (cur >= 0) {
+                st[cur & 31][lane] = p;
+                flush_block(cur & ~31, (cur & 31) + 1);
+            }
         }
     }
 }
@@ -804,7 +957,7 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     size_t    off  = 0;
     auto      take = [&](size_t floats) {
         size_t o = off;
-        off += ((floats > 0 ? floats : 1) * 4 + 255) & ~(size_t)255;
+        off += ((floats + 8) * 4 + 255) & ~(size_t)255;  // slack: empty sequences read one float
         return o;
     };
     L.A     = take((size_t)s.state_floats);
@@ -838,14 +991,14 @@ std::atomic<long long> g_launches{0};
         }                                        \
     } while (0)
 
-template <int RING>
+template <int RING, bool TILED>
 int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
                  int edges_in_smem, cudaStream_t st) {
     if (smem > 48 * 1024) {
-        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)smem));
+        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING, TILED>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    k_sweep<RING><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    k_sweep<RING, TILED><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
     COUNT_LAUNCH(1);
     return FBW_B200_OK;
 }
@@ -1048,27 +1201,46 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         int nt    = (int)((s.max_states + 31) & ~31);
         nt = nt < 64 ? 64 : (nt > 1024 ? 1024 : nt);
         const size_t limit = 227 * 1024;
-        auto need = [&](int ring, int in_smem) {
-            return (size_t)4 * ring * dpmax + (size_t)8 * smax + (size_t)4 * ((smax + 2) & ~1) +
-                   (in_smem ? (size_t)8 * s.max_edges : 0) + 16;
+        // shared memory of k_sweep: score ring, state rows (64 tiled or 2), row pointers, edges
+        auto need = [&](int ring, int tiled, int in_smem) {
+            const size_t spad = tiled ? (size_t)(smax | 1) : (size_t)smax;
+            const size_t rows = tiled ? 64 : 2;
+            return (size_t)4 * ring * dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
+                   (size_t)4 * ((smax + 2) & ~1) + (in_smem ? (size_t)8 * s.max_edges : 0) + 16;
         };
-        int ring = 8, in_smem = 1;
-        while (ring > 0 && need(ring, 1) > limit) ring = ring == 8 ? 4 : (ring == 4 ? 2 : 0);
-        if (need(ring, 1) > limit) {
-            in_smem = 0;
-            ring    = 8;
-            while (ring > 0 && need(ring, 0) > limit) ring = ring == 8 ? 4 : (ring == 4 ? 2 : 0);
-            if (need(ring, 0) > limit) return FBW_B200_TOO_LARGE;
+        // preference: edges in shared memory, then tiled state rows, then a deep score ring
+        int ring = 0, tiled = 0, in_smem = 0;
+        bool found = false;
+        for (int es = 1; es >= 0 && !found; es--) {
+            for (int tl = 1; tl >= 0 && !found; tl--) {
+                for (int rg = 8; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
+                    if (need(rg, tl, es) <= limit) {
+                        ring = rg; tiled = tl; in_smem = es; found = true;
+                    }
+                }
+            }
         }
-        const size_t smem = need(ring, in_smem);
+        if (!found) return FBW_B200_TOO_LARGE;
+        const size_t smem = need(ring, tiled, in_smem);
         const int grid = (int)(2 * s.B);
         int rc;
-        switch (ring) {
-            case 8: rc = launch_sweep<8>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
-            case 4: rc = launch_sweep<4>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
-            case 2: rc = launch_sweep<2>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
-            default: rc = launch_sweep<0>(a, grid, nt, smem, smax, dpmax, in_smem, st); break;
+#define SWEEP_CASE(R, TL) rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, st)
+        if (tiled) {
+            switch (ring) {
+                case 8: SWEEP_CASE(8, true); break;
+                case 4: SWEEP_CASE(4, true); break;
+                case 2: SWEEP_CASE(2, true); break;
+                default: SWEEP_CASE(0, true); break;
+            }
+        } else {
+            switch (ring) {
+                case 8: SWEEP_CASE(8, false); break;
+                case 4: SWEEP_CASE(4, false); break;
+                case 2: SWEEP_CASE(2, false); break;
+                default: SWEEP_CASE(0, false); break;
+            }
         }
+#undef SWEEP_CASE
         if (rc != FBW_B200_OK) return rc;
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
