@@ -36,6 +36,8 @@
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <mutex>
 
 namespace {
 
@@ -55,6 +57,7 @@ struct PlanLayout {
     size_t scount, ecount, state_off, edge_off, slot_off;                        // int[B+1]
     size_t seq_T, start_l, end_l;                                                // int[B]
     size_t ta_off, tg_off, gf_off, gu_off, pu_off;                               // i64[B+1]
+    size_t order, cost;                                                          // int[B], i64[B]
     size_t eiota, keyq, keyf, keyb, key32_out, qe, fe, be, me, slot_of_edge;     // [E]
     size_t key64, key64_out;                                                     // u64[E]
     size_t head, hs, m_ptr;                                                      // int[E+1]
@@ -111,6 +114,8 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.gf_off       = take(8 * (nB + 1));
     L.gu_off       = take(8 * (nB + 1));
     L.pu_off       = take(8 * (nB + 1));
+    L.order        = take(4 * nB);
+    L.cost         = take(8 * nB);
     L.eiota        = take(4 * nE);
     L.keyq         = take(4 * nE);
     L.keyf         = take(4 * nE);
@@ -190,6 +195,14 @@ __device__ __forceinline__ float prob_add_fast(float acc, float x) {
     if (acc == CUDART_INF_F) return prob_first(x);
     const float m = fminf(acc, x);
     if (prob_add_is_min(acc, x, m)) return m;
+    return prob_add(acc, x);
+}
+
+// prob_add(acc, x) with only the free shortcuts (+inf term, first term).  Used by the sweeps, where
+// neighbouring states' scores are close and the dominance test rarely pays for itself.
+__device__ __forceinline__ float prob_add_live(float acc, float x) {
+    if (x == CUDART_INF_F) return acc;
+    if (acc == CUDART_INF_F) return prob_first(x);
     return prob_add(acc, x);
 }
 
@@ -317,7 +330,7 @@ __global__ void k_packed(const int* __restrict__ sorted_state, i64 S, int* packe
 __global__ void k_edgekeys(const int* __restrict__ edges, i64 E, i64 F,
                            const int* __restrict__ packed_of, unsigned* keyq, unsigned* keyf,
                            unsigned* keyb, unsigned long long* key64, int* eiota, int* rowcnt_f,
-                           int* rowcnt_b, const fbw_b200_summary* hdr) {
+                           int* rowcnt_b, fbw_b200_summary* hdr) {
     if (hdr->error) return;
     i64 e = (i64)blockIdx.x * blockDim.x + threadIdx.x;
     if (e < E) {
@@ -328,8 +341,13 @@ __global__ void k_edgekeys(const int* __restrict__ edges, i64 E, i64 F,
         keyb[e]  = (unsigned)pf;
         key64[e] = (unsigned long long)sq * (unsigned long long)F + (unsigned long long)em;
         eiota[e] = (int)e;
-        atomicAdd(&rowcnt_f[pt], 1);
-        atomicAdd(&rowcnt_b[pf], 1);
+        const int din  = atomicAdd(&rowcnt_f[pt], 1) + 1;
+        const int dout = atomicAdd(&rowcnt_b[pf], 1) + 1;
+        const int deg  = din > dout ? din : dout;
+        // largest degree seen so far; the plain read keeps almost all edges off the atomic
+        if ((i64)deg > *(volatile i64*)&hdr->max_degree) {
+            atomicMax((unsigned long long*)&hdr->max_degree, (unsigned long long)deg);
+        }
     }
 }
 
@@ -361,7 +379,10 @@ __global__ void k_slots(const unsigned long long* __restrict__ key64s, const int
     }
 }
 
-// single block: everything per sequence that needs the slot counts; offsets of the run arrays
+// single block: everything per sequence that needs the slot counts.  Storage offsets of the run
+// arrays are scans in sequence order; work-item offsets (gather and posterior units) are scans in
+// RANK order, rank 0 being the most expensive sequence (frames x edges), so that kernels hand out
+// work longest-first and a contiguous rank range is a group of similar cost.
 __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off,
                                               const int* __restrict__ edge_off,
                                               const int* __restrict__ hs,
@@ -370,19 +391,23 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
                                               const int* __restrict__ packed_of, int B, i64 T,
                                               i64 F, i64 E, i64 S, int* slot_off, int* start_l,
                                               int* end_l, i64* ta_off, i64* tg_off, i64* gf_off,
-                                              i64* gu_off, i64* pu_off, fbw_b200_summary* hdr) {
+                                              i64* gu_off, i64* pu_off, i64* cost, int* order,
+                                              fbw_b200_summary* hdr) {
     typedef cub::BlockScan<i64, 1024> Scan;
     __shared__ typename Scan::TempStorage tmp;
     __shared__ i64 carry[6];
     __shared__ int smax[4];
+    __shared__ int gmax[3][FBW_B200_GROUPS];
     if (threadIdx.x < 6) carry[threadIdx.x] = 0;
     if (threadIdx.x < 4) smax[threadIdx.x] = 0;
+    if (threadIdx.x < 3 * FBW_B200_GROUPS) (&gmax[0][0])[threadIdx.x] = 0;
     __syncthreads();
     const bool bad = hdr->error != 0;
+    // ---- per sequence, sequence order: storage offsets, maxima, cost ----
     for (int base = 0; base < B; base += 1024) {
         int  b  = base + threadIdx.x;
         bool ok = b < B;
-        i64  v[6] = {0, 0, 0, 0, 0, 0};
+        i64  v[4] = {0, 0, 0, 0};
         if (ok) {
             int Sb = state_off[b + 1] - state_off[b];
             int Eb = edge_off[b + 1] - edge_off[b];
@@ -399,43 +424,88 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
             v[0] = (i64)nt * Sb * kTile;
             v[1] = (i64)nt * Db * kTile;
             v[2] = (i64)Te * Dp;
-            v[3] = (i64)nt * ((Db + kGatherSlots - 1) / kGatherSlots);
-            v[4] = nt;
-            v[5] = Te;
+            v[3] = Te;
+            cost[b] = (i64)Te * (Eb + 1);
             atomicMax(&smax[0], Sb);
             atomicMax(&smax[1], Eb);
             atomicMax(&smax[2], Db);
             atomicMax(&smax[3], Te);
         }
-        i64* dst[5] = {ta_off, tg_off, gf_off, gu_off, pu_off};
-        for (int k = 0; k < 6; k++) {
+        i64* dst[3] = {ta_off, tg_off, gf_off};
+        for (int k = 0; k < 4; k++) {
             i64 ex, agg;
             Scan(tmp).ExclusiveSum(v[k], ex, agg);
-            if (ok && k < 5) dst[k][b] = carry[k] + ex;
+            if (ok && k < 3) dst[k][b] = carry[k] + ex;
             __syncthreads();
             if (threadIdx.x == 0) carry[k] += agg;
             __syncthreads();
         }
     }
+    if (threadIdx.x == 0) slot_off[B] = hs[E];
+    __syncthreads();
+    // ---- rank by descending cost (ties: ascending sequence id) ----
+    for (int b = threadIdx.x; b < B; b += 1024) {
+        const i64 cb = cost[b];
+        int rank = 0;
+        for (int j = 0; j < B; j++) {
+            const i64 cj = cost[j];
+            rank += (cj > cb || (cj == cb && j < b)) ? 1 : 0;
+        }
+        order[rank] = b;
+    }
+    __syncthreads();
+    // ---- work-item offsets in rank order ----
+    for (int base = 0; base < B; base += 1024) {
+        int  r  = base + threadIdx.x;
+        bool ok = r < B;
+        i64  v[2] = {0, 0};
+        if (ok) {
+            int b  = order[r];
+            int Db = slot_off[b + 1] - slot_off[b];
+            int nt = (seq_T[b] + kTile - 1) / kTile;
+            v[0] = (i64)nt * ((Db + kGatherSlots - 1) / kGatherSlots);
+            v[1] = nt;
+            int g = 0;  // group of rank r: groups are the rank ranges [g*B/G, (g+1)*B/G)
+            for (int q = 1; q < FBW_B200_GROUPS; q++) {
+                if (r >= (int)(((i64)q * B) / FBW_B200_GROUPS)) g = q;
+            }
+            atomicMax(&gmax[0][g], state_off[b + 1] - state_off[b]);
+            atomicMax(&gmax[1][g], edge_off[b + 1] - edge_off[b]);
+            atomicMax(&gmax[2][g], Db);
+        }
+        i64* dst[2] = {gu_off, pu_off};
+        for (int k = 0; k < 2; k++) {
+            i64 ex, agg;
+            Scan(tmp).ExclusiveSum(v[k], ex, agg);
+            if (ok) dst[k][r] = carry[4 + k] + ex;
+            __syncthreads();
+            if (threadIdx.x == 0) carry[4 + k] += agg;
+            __syncthreads();
+        }
+    }
     if (threadIdx.x == 0) {
-        slot_off[B] = hs[E];
         ta_off[B] = carry[0];
         tg_off[B] = carry[1];
         gf_off[B] = carry[2];
-        gu_off[B] = carry[3];
-        pu_off[B] = carry[4];
+        gu_off[B] = carry[4];
+        pu_off[B] = carry[5];
         hdr->T = T; hdr->B = B; hdr->F = F; hdr->E = E; hdr->S = S;
         hdr->state_floats = carry[0];
         hdr->tiled_floats = carry[1];
         hdr->frame_floats = carry[2];
-        hdr->gather_units = carry[3];
-        hdr->post_units   = carry[4];
-        hdr->sum_len      = carry[5];
+        hdr->sum_len      = carry[3];
+        hdr->gather_units = carry[4];
+        hdr->post_units   = carry[5];
         hdr->num_slots    = hs[E];
         hdr->max_states = smax[0];
         hdr->max_edges  = smax[1];
         hdr->max_slots  = smax[2];
         hdr->max_len    = smax[3];
+        for (int g = 0; g < FBW_B200_GROUPS; g++) {
+            hdr->group_max_states[g] = gmax[0][g];
+            hdr->group_max_edges[g]  = gmax[1][g];
+            hdr->group_max_slots[g]  = gmax[2][g];
+        }
         if (smax[0] > kMaxPerSeq || smax[2] > kMaxPerSeq) {
             hdr->error |= FBW_B200_ERR_SEQ_TOO_LARGE;
         }
@@ -481,14 +551,15 @@ struct RunArgs {
     float*       sums;
     float*       loss2;
     float *A, *Bt, *Gt, *Gf, *P;
+    int* status;  // device status word of the call (0 = ok)
     const int *state_off, *edge_off, *slot_off, *seq_T, *start_l, *end_l;
     const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off;
     const int *rowptr_f, *rowptr_b;
     const uint2 *fwd_rec, *bwd_rec;
     const int4 *q_rec, *m_rec;
-    const int *m_ptr, *slot_emis;
+    const int *m_ptr, *slot_emis, *order;
     i64 T, B, F;
-    i64 gather_units, post_units;
+    int r0, r1;  // rank range (a group of sequences) this launch works on
 };
 
 // Gather am_scores[t,b,emission] for the distinct emissions ("slots", ascending emission id) of
@@ -499,9 +570,11 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
     __shared__ float tile[kTile][kGatherSlots + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int B = (int)a.B;
-    for (i64 u = blockIdx.x; u < a.gather_units; u += gridDim.x) {
-        const int b   = find_seq(a.gu_off, B, u);
-        const int r   = (int)(u - a.gu_off[b]);
+    const i64 u_end = a.gu_off[a.r1];
+    for (i64 u = a.gu_off[a.r0] + blockIdx.x; u < u_end; u += gridDim.x) {
+        const int rk  = find_seq(a.gu_off, B, u);
+        const int b   = a.order[rk];
+        const int r   = (int)(u - a.gu_off[rk]);
         const int so  = a.slot_off[b];
         const int Db  = a.slot_off[b + 1] - so;
         const int Dp  = (Db + 3) & ~3;
@@ -548,7 +621,6 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
     }
 }
 
-constexpr int kRegEdges = 4;  // in-edges (out-edges backward) of a thread's state kept in registers
 
 // One persistent CTA per (sequence, direction).  Shared memory holds the sequence's sorted edge list
 // (target-sorted for the forward sweep, source-sorted for the backward one), the state-score
@@ -561,11 +633,12 @@ constexpr int kRegEdges = 4;  // in-edges (out-edges backward) of a thread's sta
 // tile is written out as full 128-byte lines; otherwise every frame's vector is scattered out.
 // Replaces set_start_states / init_bwd_state_buffer / next_frame / fill_array and the two host loops
 // (fbw_op.cu:17-29, 61-102, 297-353).
-template <int RING, bool TILED>
+// KREG: edges of a thread's state kept in registers (further edges are read from the list).
+template <int RING, bool TILED, int KREG>
 __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int item = blockIdx.x;
-    const int b    = item >> 1;
+    const int b    = a.order[a.r0 + (item >> 1)];  // most expensive sequences first
     const bool fwd = (item & 1) == 0;
     const int  Te  = a.seq_T[b];
     if (Te == 0) return;
@@ -576,6 +649,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     const int NT = blockDim.x, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
     constexpr int kRows = TILED ? 64 : 2;
+    constexpr int kRegEdges = KREG;
     const int spad = TILED ? (smax | 1) : smax;  // odd row stride: conflict-free transposed reads
 
     float* ring  = reinterpret_cast<float*>(smem_raw);                      // RING * dpmax
@@ -680,12 +754,12 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
                 }
                 float acc = CUDART_INF_F;
 #pragma unroll
-                for (int k = 0; k < kRegEdges; k++) acc = prob_add_fast(acc, v[k]);
+                for (int k = 0; k < kRegEdges; k++) acc = prob_add_live(acc, v[k]);
                 for (int i = xi0; i < xi1; i++) {
                     const uint2 r  = recs[i];
                     const float pv = cur[r.x & 0xffffu];
                     if (!isinf(pv)) {
-                        acc = prob_add_fast(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
+                        acc = prob_add_live(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
                     }
                 }
                 nxt[tid] = acc;
@@ -697,7 +771,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
                     const uint2 r  = recs[i];
                     const float pv = cur[r.x & 0xffffu];
                     if (!isinf(pv)) {
-                        acc = prob_add_fast(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
+                        acc = prob_add_live(acc, (pv + __uint_as_float(r.y)) + g[r.x >> 16]);
                     }
                 }
                 nxt[s] = acc;
@@ -716,24 +790,87 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     if (RING > 0) cp_async_wait<0>();
 }
 
-constexpr int kPostChunk = 8;  // edges whose loads are in flight while the previous 8 are folded
+// ---- bulk-copy (TMA) helpers: 1-D cp.async.bulk global -> shared, completion on an mbarrier ----
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// both addresses 16-byte aligned, bytes a multiple of 16
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
+                                         unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 
-// Edge scores, normaliser and class posteriors; one warp per (sequence, 32-frame tile), lane = frame.
-// For frame t:  x_e = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)   (fbw_op.cu:93-100)
+// named barriers (ids 1..15; 0 is __syncthreads): sync waits, arrive only signals
+// The id is an immediate so that the compiler can count the barriers a CTA really uses (a register
+// id makes it reserve all 16, which caps the resident CTAs per SM).
+template <int ID>
+__device__ __forceinline__ void named_sync(int count) {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(count) : "memory");
+}
+template <int ID>
+__device__ __forceinline__ void named_arrive(int count) {
+    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "r"(count) : "memory");
+}
+
+constexpr int kPostEdges = 40;  // edges per chunk of the normaliser fold (5 batches)
+constexpr int kPostBatch = 8;   // edges whose lines are loaded together
+struct __align__(16) PostSmem {
+    float x[2][kPostEdges][kTile];        // edge scores, [buffer][edge][frame]
+    float stage[2][kTile][kTile + 1];     // per-warp posterior transpose
+    float acc[kTile];                     // the frame normalisers, handed from warp 0 to warp 1
+};
+
+// Edge scores, normaliser and class posteriors; one CTA of two warps per (sequence, 32-frame tile),
+// lane = frame.  For frame t:
+//   x_e  = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)              (fbw_op.cu:93-100)
 //   sum  = left fold of prob_add over the sequence's edges in ascending edge index (fbw_op.cu:115-118)
 //   sums[t,b] = isinf(sum) ? 0 : sum                                              (fbw_op.cu:120-129)
-//   post[t][slot] = fold over the slot's edges of (x_e - sum)                     (fbw_op.cu:131-153)
-// The tiled layouts make every load of a warp one 128-byte line.  Loads of the next chunk of edges
-// are issued before the current chunk is folded, so the serial fold never waits on memory; steps
-// whose result is provably the running minimum in every lane skip expf/log1pf.
-__global__ void __launch_bounds__(128, 4) k_post(RunArgs a) {
-    __shared__ float stage[4][kTile][kTile + 1];
+//   post[t][slot] = -log sum over the slot's edges of exp(-(x_e - sum))           (fbw_op.cu:131-153)
+// In the tiled layouts the 32 frames of one state (or slot) are one 128-byte line, so every load of a
+// warp is one line.  The fold is the only serial part: warp 1 computes the edge scores 32 edges
+// ahead into a double buffer in shared memory, warp 0 only folds them (steps whose result is
+// provably the running minimum in every lane skip expf/log1pf).  The class posteriors are then
+// split between both warps by blocks of 32 slots.
+__global__ void __launch_bounds__(64, 10) k_post(RunArgs a) {
+    __shared__ PostSmem sm;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int B = (int)a.B;
-    float (*st)[kTile + 1] = stage[warp];
-    for (i64 u = (i64)blockIdx.x * 4 + warp; u < a.post_units; u += (i64)gridDim.x * 4) {
-        const int b  = find_seq(a.pu_off, B, u);
-        const int k  = (int)(u - a.pu_off[b]);
+
+    // Units are in descending cost order.  CTA w takes units w, 2W-1-w, 2W+w, 4W-1-w, ...: a CTA
+    // that drew an expensive unit in one round draws a cheap one in the next.
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    const i64 W = gridDim.x, w = blockIdx.x;
+    for (i64 round = 0; round * W < nunits; round++) {
+        const i64 idx = (round & 1) ? (round + 1) * W - 1 - w : round * W + w;
+        if (idx >= nunits) continue;  // uniform in the CTA
+        const i64 u  = u0 + idx;
+        const int rk = find_seq(a.pu_off, B, u);
+        const int b  = a.order[rk];
+        const int k  = (int)(u - a.pu_off[rk]);
         const int Sb = a.state_off[b + 1] - a.state_off[b];
         const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
         const int so = a.slot_off[b], Db = a.slot_off[b + 1] - so;
@@ -742,103 +879,124 @@ __global__ void __launch_bounds__(128, 4) k_post(RunArgs a) {
         const int t  = k * kTile + lane;
         const bool valid = t < Te;
         // every lane loads (the tile is allocated for all 32 frames); lanes past the sequence's
-        // length read unspecified values and are forced to +inf below
+        // length read unspecified values and are forced to +inf
         const float* __restrict__ Ab = a.A + a.ta_off[b] + (i64)k * Sb * kTile + lane;
         const float* __restrict__ Bb = a.Bt + a.ta_off[b] + (i64)k * Sb * kTile + lane;
         const float* __restrict__ Gb = a.Gt + a.tg_off[b] + (i64)k * Db * kTile + lane;
 
-        // raw operands of a chunk of edges: straight-line loads, no control flow between them,
-        // so all of a chunk's loads are in flight together
-        struct Chunk {
-            float al[kPostChunk], be[kPostChunk], g[kPostChunk], w[kPostChunk];
-            int   sl[kPostChunk];
-        };
-        auto load_chunk = [&](const int4* __restrict__ recs, int i0, Chunk& c) {
-            int4 r[kPostChunk];
+        // scores of edges recs[i0 .. i0+kPostBatch): all loads first (straight-line, so they are in
+        // flight together), then the arithmetic.  The reference writes +inf for an edge whose
+        // source (forward) or target (backward) state is unreachable (fbw_op.cu:82-85).
+        auto batch_scores = [&](const int4* __restrict__ recs, int i0, int iend, float* x, int* sl) {
+            int4  r[kPostBatch];
+            float al[kPostBatch], be[kPostBatch], g[kPostBatch];
 #pragma unroll
-            for (int j = 0; j < kPostChunk; j++) {
-                r[j] = __ldg(recs + min(i0 + j, Eb - 1));
+            for (int j = 0; j < kPostBatch; j++) r[j] = __ldg(recs + min(i0 + j, iend - 1));
+#pragma unroll
+            for (int j = 0; j < kPostBatch; j++) {
+                al[j] = Ab[r[j].x * kTile];
+                be[j] = Bb[r[j].y * kTile];
+                g[j]  = Gb[r[j].z * kTile];
             }
 #pragma unroll
-            for (int j = 0; j < kPostChunk; j++) {
-                c.al[j] = Ab[(i64)r[j].x * kTile];
-                c.be[j] = Bb[(i64)r[j].y * kTile];
-                c.g[j]  = Gb[(i64)r[j].z * kTile];
-                c.w[j]  = __int_as_float(r[j].w);
-                c.sl[j] = i0 + j < Eb ? r[j].z : -1;
+            for (int j = 0; j < kPostBatch; j++) {
+                // an unreachable source or target state has score +inf and the sum is +inf, which
+                // is what the reference stores for such an edge (fbw_op.cu:82-85)
+                const float v = ((al[j] + __int_as_float(r[j].w)) + g[j]) + be[j];
+                x[j]  = (!valid || i0 + j >= iend) ? CUDART_INF_F : v;
+                sl[j] = i0 + j < iend ? r[j].z : -1;
             }
-        };
-        // the reference writes +inf for an edge whose source (forward) or target (backward) state
-        // is unreachable (fbw_op.cu:82-85) before any addition
-        auto score = [&](const Chunk& c, int j) -> float {
-            const float x = ((c.al[j] + c.w[j]) + c.g[j]) + c.be[j];
-            const bool dead = !valid || c.sl[j] < 0 || isinf(c.al[j]) || isinf(c.be[j]);
-            return dead ? CUDART_INF_F : x;
         };
 
-        // ---- normaliser: serial left fold in ascending edge index -------------------------------
-        float acc = CUDART_INF_F;
-        if (Eb > 0) {
-            const int4* __restrict__ q = a.q_rec + e0;
-            Chunk nx;
-            load_chunk(q, 0, nx);
-            for (int i0 = 0; i0 < Eb; i0 += kPostChunk) {
-                float x[kPostChunk];
+        // ---- normaliser ------------------------------------------------------------------------
+        // Both warps compute the edge scores of a chunk into shared memory (warp 0 two batches,
+        // warp 1 three); after the barrier warp 0 folds the chunk in ascending edge index while
+        // warp 1 already loads the next one.  One barrier per chunk orders everything: a buffer is
+        // rewritten two chunks later, after a barrier that warp 0 reaches only when its fold is done.
+        const int4* __restrict__ q = a.q_rec + e0;
+        const int nchunks = (Eb + kPostEdges - 1) / kPostEdges;
+        float facc = CUDART_INF_F;
+        for (int c = 0; c < nchunks; c++) {
+            const int i0 = c * kPostEdges, i1 = min(i0 + kPostEdges, Eb);
+            const int b_lo = warp == 0 ? 0 : 2, b_hi = warp == 0 ? 2 : kPostEdges / kPostBatch;
+            for (int bb = b_lo; bb < b_hi; bb++) {
+                const int i = i0 + bb * kPostBatch;
+                if (i >= i1) break;
+                float x[kPostBatch];
+                int   sl[kPostBatch];
+                batch_scores(q, i, i1, x, sl);
 #pragma unroll
-                for (int j = 0; j < kPostChunk; j++) x[j] = score(nx, j);
-                if (i0 + kPostChunk < Eb) load_chunk(q, i0 + kPostChunk, nx);
-#pragma unroll
-                for (int j = 0; j < kPostChunk; j++) acc = prob_add_fast(acc, x[j]);
+                for (int j = 0; j < kPostBatch; j++) {
+                    if (i + j < i1) sm.x[c & 1][i - i0 + j][lane] = x[j];
+                }
+            }
+            __syncthreads();
+            if (warp == 0) {
+                const int ne = i1 - i0;
+                for (int j = 0; j < ne; j++) facc = prob_add_fast(facc, sm.x[c & 1][j][lane]);
             }
         }
-        if (valid) a.sums[(i64)t * B + b] = isinf(acc) ? 0.f : acc;
+        if (warp == 0) {
+            if (valid) a.sums[(i64)t * B + b] = isinf(facc) ? 0.f : facc;
+            sm.acc[lane] = facc;
+        }
+        __syncthreads();
+        const float acc = sm.acc[lane];
 
-        // ---- class posteriors: edges in (slot, edge index) order ---------------------------------
-        float* __restrict__ Pb = a.P + a.gf_off[b];
-        auto flush_block = [&](int d0, int nd) {  // slots d0..d0+nd-1 are staged: transpose out
+        // ---- class posteriors: blocks of 32 slots alternate between the two warps ----------------
+        // Per slot: -log sum_e exp(-(x_e - sum)) as a running (minimum, scaled sum) pair.  The terms
+        // are normalised (magnitude of a log-posterior), so a fast exponential is accurate to ~1e-7
+        // in the posterior; the reference accumulates the same terms with atomics in no fixed order
+        // (fbw_op.cu:137-153).  A slot with one edge gets x_e - sum exactly.
+        const int4* __restrict__ m  = a.m_rec + e0;
+        const int* __restrict__ mp  = a.m_ptr + so;
+        float* __restrict__ Pb      = a.P + a.gf_off[b];
+        float (*st)[kTile + 1]      = sm.stage[warp];
+        const bool rowdead = !(acc < CUDART_INF_F);  // no path through this frame
+        const int  mbase   = mp[0];                  // position of the sequence's first edge
+        for (int d0 = warp * kTile; d0 < Db; d0 += 2 * kTile) {
+            const int nd = min(kTile, Db - d0);
+            const int j0 = mp[d0] - mbase, j1 = mp[d0 + nd] - mbase;
+            int   cur = -1;
+            float mn = CUDART_INF_F, sme = 1.f;
+            for (int i = j0; i < j1; i += kPostBatch) {
+                float x[kPostBatch];
+                int   sl[kPostBatch];
+                batch_scores(m, i, j1, x, sl);
+#pragma unroll
+                for (int j = 0; j < kPostBatch; j++) {
+                    if (sl[j] < 0) continue;  // past the end of the block (uniform)
+                    const float y = x[j] - acc;  // +inf for dead edges; NaN only if the row is dead
+                    if (sl[j] != cur) {          // uniform: a new slot starts
+                        if (cur >= 0) {
+                            st[cur - d0][lane] =
+                                (mn == CUDART_INF_F || rowdead) ? CUDART_INF_F : mn - logf(sme);
+                        }
+                        cur = sl[j];
+                        mn  = y;
+                        sme = 1.f;
+                    } else if (y < CUDART_INF_F) {
+                        if (y < mn) {
+                            sme = sme * __expf(y - mn) + 1.f;  // exp(-inf) = 0 if mn was +inf
+                            mn  = y;
+                        } else {
+                            sme += __expf(mn - y);
+                        }
+                    }
+                }
+            }
+            if (cur >= 0) {
+                st[cur - d0][lane] = (mn == CUDART_INF_F || rowdead) ? CUDART_INF_F : mn - logf(sme);
+            }
             __syncwarp();
+            // transpose: frame r of the tile gets its nd posteriors as one contiguous write
             for (int r = 0; r < kTile; r++) {
                 const int tr = k * kTile + r;
                 if (tr < Te && lane < nd) Pb[(i64)tr * Dp + d0 + lane] = st[lane][r];
             }
             __syncwarp();
-        };
-        if (Eb > 0) {
-            const int4* __restrict__ m = a.m_rec + e0;
-            Chunk nx;
-            load_chunk(m, 0, nx);
-            int   cur = -1;
-            float p   = CUDART_INF_F;
-            for (int i0 = 0; i0 < Eb; i0 += kPostChunk) {
-                float y[kPostChunk];
-                int   s[kPostChunk];
-#pragma unroll
-                for (int j = 0; j < kPostChunk; j++) {
-                    y[j] = score(nx, j) - acc;
-                    s[j] = nx.sl[j];
-                }
-                if (i0 + kPostChunk < Eb) load_chunk(m, i0 + kPostChunk, nx);
-#pragma unroll
-                for (int j = 0; j < kPostChunk; j++) {
-                    if (s[j] < 0) continue;  // past the end (uniform)
-                    if (s[j] != cur) {       // uniform: a new slot starts
-                        if (cur >= 0) {
-                            st[cur & 31][lane] = p;
-                            if ((cur & 31) == 31) flush_block(cur & ~31, 32);
-                        }
-                        cur = s[j];
-                        p   = prob_first(y[j]);
-                    } else {
-                        // prob_add(p, y) with the exact shortcuts; y may be NaN (inf - inf)
-                        p = (p == CUDART_INF_F) ? prob_first(y[j]) : prob_add_fast(p, y[j]);
-                    }
-                }
-            }
-            if (cur >= 0) {
-                st[cur & 31][lane] = p;
-                flush_block(cur & ~31, (cur & 31) + 1);
-            }
         }
+        __syncthreads();  // sm.x / sm.acc are reused by the next unit
     }
 }
 
@@ -856,10 +1014,12 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
     float* seg = segs[warp];
     for (int i = lane; i < kSegFloats; i += 32) seg[i] = CUDART_INF_F;
     __syncwarp();
-    const i64 rows = a.T * a.B;
-    for (i64 r = (i64)blockIdx.x * 8 + warp; r < rows; r += (i64)gridDim.x * 8) {
-        const int  t  = (int)(r / B);
-        const int  b  = (int)(r - (i64)t * B);
+    const int nb  = a.r1 - a.r0;  // sequences of this group
+    const i64 rows = a.T * nb;
+    for (i64 i = (i64)blockIdx.x * 8 + warp; i < rows; i += (i64)gridDim.x * 8) {
+        const int  t  = (int)(i / nb);
+        const int  b  = a.order[a.r0 + (int)(i - (i64)t * nb)];
+        const i64  r  = (i64)t * B + b;
         const bool valid = t < a.seq_T[b];
         const int  so = a.slot_off[b];
         const int  Db = valid ? a.slot_off[b + 1] - so : 0;
@@ -949,7 +1109,7 @@ __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i
 // host side
 // ---------------------------------------------------------------------------------------------
 struct RunLayout {
-    size_t A, Bt, Gt, Gf, P, total;
+    size_t status, A, Bt, Gt, Gf, P, total;
 };
 
 RunLayout run_layout(const fbw_b200_summary& s) {
@@ -960,6 +1120,7 @@ RunLayout run_layout(const fbw_b200_summary& s) {
         off += ((floats + 8) * 4 + 255) & ~(size_t)255;  // slack: empty sequences read one float
         return o;
     };
+    L.status = take(56);
     L.A     = take((size_t)s.state_floats);
     L.Bt    = take((size_t)s.state_floats);
     L.Gt    = take((size_t)s.tiled_floats);
@@ -991,15 +1152,161 @@ std::atomic<long long> g_launches{0};
         }                                        \
     } while (0)
 
-template <int RING, bool TILED>
-int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
-                 int edges_in_smem, cudaStream_t st) {
+template <int RING, bool TILED, int KREG>
+int launch_sweep_k(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
+                   int edges_in_smem, cudaStream_t st) {
     if (smem > 48 * 1024) {
-        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING, TILED>,
+        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING, TILED, KREG>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-    k_sweep<RING, TILED><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    k_sweep<RING, TILED, KREG><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
     COUNT_LAUNCH(1);
+    return FBW_B200_OK;
+}
+
+template <int RING, bool TILED>
+int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
+                 int edges_in_smem, int degree, cudaStream_t st) {
+    if (degree <= 2) return launch_sweep_k<RING, TILED, 2>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    if (degree <= 3) return launch_sweep_k<RING, TILED, 3>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    return launch_sweep_k<RING, TILED, 4>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+}
+
+// streams and events for the per-group pipelines, one pool per device, created on first use
+struct StreamPool {
+    std::mutex   mu;
+    bool         ready = false, failed = false;
+    cudaStream_t aux[FBW_B200_GROUPS];
+    cudaEvent_t  fork, join[FBW_B200_GROUPS];
+};
+StreamPool g_pools[64];
+std::mutex g_pools_mu;
+
+StreamPool* stream_pool() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    StreamPool* p = &g_pools[dev];
+    std::lock_guard<std::mutex> lk(g_pools_mu);
+    if (p->failed) return nullptr;
+    if (!p->ready) {
+        bool ok = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < FBW_B200_GROUPS && ok; i++) {
+            ok = cudaStreamCreateWithFlags(&p->aux[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&p->join[i], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!ok) {
+            p->failed = true;
+            return nullptr;
+        }
+        p->ready = true;
+    }
+    return p;
+}
+
+// number of launch groups (1, 2, 4 or 8): small calls stay on one stream
+int choose_groups(const fbw_b200_summary& s) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("FBW_B200_NUM_GROUPS");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
+    const double cells = (double)s.T * (double)s.B * (double)s.F;
+    if (s.B >= 32 && cells >= 2.5e8) return 8;
+    if (s.B >= 16 && cells >= 1.0e8) return 4;
+    return 1;
+}
+
+// gather -> sweep -> posterior -> expand for the sequences of ranks [r0, r1) on stream st.
+// ms/me/md: largest state, edge and slot counts in the range (they size the sweep launch).
+int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b200_summary& s,
+                 cudaStream_t st, cudaEvent_t* ev) {
+    const int sms = sm_count();
+    const int nb  = r1 - r0;
+    a.r0 = r0;
+    a.r1 = r1;
+    const i64 tiles = (s.max_len + kTile - 1) / kTile;
+    if (ev) CUDA_OK(cudaEventRecord(ev[0], st));
+    if (s.gather_units > 0 && md > 0) {
+        i64 want = tiles * nb * ((md + kGatherSlots - 1) / kGatherSlots);
+        int grid = (int)(want < (i64)sms * 6 ? want : (i64)sms * 6);
+        k_gather<<<grid > 0 ? grid : 1, 256, 0, st>>>(a);
+        COUNT_LAUNCH(1);
+    }
+    if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
+    if (s.max_len > 0) {
+        int smax  = (int)((ms + 3) & ~3);
+        int dpmax = (int)((md + 3) & ~3);
+        int nt    = (int)((ms + 31) & ~31);
+        nt = nt < 64 ? 64 : (nt > 1024 ? 1024 : nt);
+        const size_t limit = 227 * 1024;
+        // shared memory of k_sweep: score ring, state rows (64 tiled or 2), row pointers, edges
+        auto need = [&](int ring, int tiled, int in_smem) {
+            const size_t spad = tiled ? (size_t)(smax | 1) : (size_t)smax;
+            const size_t rows = tiled ? 64 : 2;
+            return (size_t)4 * ring * dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
+                   (size_t)4 * ((smax + 2) & ~1) + (in_smem ? (size_t)8 * me : 0) + 16;
+        };
+        // preference: edges in shared memory, then tiled state rows, then a deep score ring
+        int ring = 0, tiled = 0, in_smem = 0;
+        bool found = false;
+        for (int es = 1; es >= 0 && !found; es--) {
+            for (int tl = 1; tl >= 0 && !found; tl--) {
+                for (int rg = 8; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
+                    if (need(rg, tl, es) <= limit) {
+                        ring = rg; tiled = tl; in_smem = es; found = true;
+                    }
+                }
+            }
+        }
+        if (!found) return FBW_B200_TOO_LARGE;
+        const size_t smem = need(ring, tiled, in_smem);
+        const int grid = 2 * nb;
+        int rc;
+#define SWEEP_CASE(R, TL) \
+    rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, (int)s.max_degree, st)
+        if (tiled) {
+            switch (ring) {
+                case 8: SWEEP_CASE(8, true); break;
+                case 4: SWEEP_CASE(4, true); break;
+                case 2: SWEEP_CASE(2, true); break;
+                default: SWEEP_CASE(0, true); break;
+            }
+        } else {
+            switch (ring) {
+                case 8: SWEEP_CASE(8, false); break;
+                case 4: SWEEP_CASE(4, false); break;
+                case 2: SWEEP_CASE(2, false); break;
+                default: SWEEP_CASE(0, false); break;
+            }
+        }
+#undef SWEEP_CASE
+        if (rc != FBW_B200_OK) return rc;
+    }
+    if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
+    if (s.post_units > 0) {
+        // two-warp CTAs, one unit at a time each; all resident at once where possible.  The kernel
+        // needs the large shared-memory carveout to reach ten CTAs per SM.
+        static bool carve_set[64] = {false};
+        int dev = 0;
+        CUDA_OK(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !carve_set[dev]) {
+            CUDA_OK(cudaFuncSetAttribute(k_post, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
+            if (dev >= 0 && dev < 64) carve_set[dev] = true;
+        }
+        i64 want = tiles * nb;
+        int grid = (int)(want < (i64)sms * 12 ? want : (i64)sms * 12);
+        k_post<<<grid > 0 ? grid : 1, 64, 0, st>>>(a);
+        COUNT_LAUNCH(1);
+    }
+    if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
+    {
+        i64 want = (s.T * nb + 7) / 8;
+        int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
+        k_expand<<<grid, 256, 0, st>>>(a);
+        COUNT_LAUNCH(1);
+    }
     return FBW_B200_OK;
 }
 
@@ -1116,7 +1423,8 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
                                at<int>(plan, L.slot_off), at<int>(plan, L.start_l),
                                at<int>(plan, L.end_l), at<i64>(plan, L.ta_off),
                                at<i64>(plan, L.tg_off), at<i64>(plan, L.gf_off),
-                               at<i64>(plan, L.gu_off), at<i64>(plan, L.pu_off), hdr);
+                               at<i64>(plan, L.gu_off), at<i64>(plan, L.pu_off),
+                               at<i64>(plan, L.cost), at<int>(plan, L.order), hdr);
     if (E > 0) {
         k_records<<<blocks(E), TB, 0, st>>>(
             edges, weights, E, at<int>(plan, L.packed_of), at<int>(plan, L.state_off),
@@ -1161,6 +1469,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.Gt = at<float>(work, R.Gt);
     a.Gf = at<float>(work, R.Gf);
     a.P  = at<float>(work, R.P);
+    a.status = at<int>(work, R.status);
     a.state_off = at<int>(plan, L.state_off);
     a.edge_off  = at<int>(plan, L.edge_off);
     a.slot_off  = at<int>(plan, L.slot_off);
@@ -1180,82 +1489,52 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.m_rec    = at<int4>(plan, L.m_rec);
     a.m_ptr     = at<int>(plan, L.m_ptr);
     a.slot_emis = at<int>(plan, L.slot_emis);
+    a.order     = at<int>(plan, L.order);
     a.T = s.T; a.B = s.B; a.F = s.F;
-    a.gather_units = s.gather_units;
-    a.post_units   = s.post_units;
+    a.r0 = 0; a.r1 = (int)s.B;
 
-    const int sms = sm_count();
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
+    CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
 
-    if (ev) CUDA_OK(cudaEventRecord(ev[0], st));
-    if (s.gather_units > 0) {
-        int grid = (int)(s.gather_units < (i64)sms * 6 ? s.gather_units : (i64)sms * 6);
-        k_gather<<<grid, 256, 0, st>>>(a);
-        COUNT_LAUNCH(1);
-    }
-    if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
-    if (s.max_len > 0) {
-        int smax  = (int)((s.max_states + 3) & ~3);
-        int dpmax = (int)((s.max_slots + 3) & ~3);
-        int nt    = (int)((s.max_states + 31) & ~31);
-        nt = nt < 64 ? 64 : (nt > 1024 ? 1024 : nt);
-        const size_t limit = 227 * 1024;
-        // shared memory of k_sweep: score ring, state rows (64 tiled or 2), row pointers, edges
-        auto need = [&](int ring, int tiled, int in_smem) {
-            const size_t spad = tiled ? (size_t)(smax | 1) : (size_t)smax;
-            const size_t rows = tiled ? 64 : 2;
-            return (size_t)4 * ring * dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
-                   (size_t)4 * ((smax + 2) & ~1) + (in_smem ? (size_t)8 * s.max_edges : 0) + 16;
-        };
-        // preference: edges in shared memory, then tiled state rows, then a deep score ring
-        int ring = 0, tiled = 0, in_smem = 0;
-        bool found = false;
-        for (int es = 1; es >= 0 && !found; es--) {
-            for (int tl = 1; tl >= 0 && !found; tl--) {
-                for (int rg = 8; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
-                    if (need(rg, tl, es) <= limit) {
-                        ring = rg; tiled = tl; in_smem = es; found = true;
-                    }
-                }
-            }
-        }
-        if (!found) return FBW_B200_TOO_LARGE;
-        const size_t smem = need(ring, tiled, in_smem);
-        const int grid = (int)(2 * s.B);
-        int rc;
-#define SWEEP_CASE(R, TL) rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, st)
-        if (tiled) {
-            switch (ring) {
-                case 8: SWEEP_CASE(8, true); break;
-                case 4: SWEEP_CASE(4, true); break;
-                case 2: SWEEP_CASE(2, true); break;
-                default: SWEEP_CASE(0, true); break;
-            }
+    // Sequence groups (rank ranges of similar cost) run as independent pipelines
+    // gather -> sweep -> posterior -> expand on their own streams: the sweeps of cheap groups end
+    // early and their memory-bound output pass overlaps the arithmetic-bound sweep of the
+    // expensive ones.  With phase events everything runs as one group on the caller's stream.
+    int G = ev ? 1 : choose_groups(s);
+    StreamPool* pool = nullptr;
+    std::unique_lock<std::mutex> lock;
+    if (G > 1) {
+        pool = stream_pool();
+        if (!pool) {
+            G = 1;
         } else {
-            switch (ring) {
-                case 8: SWEEP_CASE(8, false); break;
-                case 4: SWEEP_CASE(4, false); break;
-                case 2: SWEEP_CASE(2, false); break;
-                default: SWEEP_CASE(0, false); break;
-            }
+            lock = std::unique_lock<std::mutex>(pool->mu);
+            CUDA_OK(cudaEventRecord(pool->fork, st));
         }
-#undef SWEEP_CASE
+    }
+    const int per = FBW_B200_GROUPS / G;  // base groups merged into one launch group
+    for (int g = 0; g < G; g++) {
+        const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
+        const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
+        if (r1 <= r0) continue;
+        i64 ms = 0, me = 0, md = 0;
+        for (int q = g * per; q < (g + 1) * per; q++) {
+            ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
+            me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
+            md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
+        }
+        cudaStream_t gs = st;
+        if (g > 0) {
+            gs = pool->aux[g];
+            CUDA_OK(cudaStreamWaitEvent(gs, pool->fork, 0));
+        }
+        int rc = launch_group(a, r0, r1, ms, me, md, s, gs, ev);
         if (rc != FBW_B200_OK) return rc;
-    }
-    if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
-    if (s.post_units > 0) {
-        i64 want = (s.post_units + 3) / 4;
-        int grid = (int)(want < (i64)sms * 16 ? want : (i64)sms * 16);
-        k_post<<<grid, 128, 0, st>>>(a);
-        COUNT_LAUNCH(1);
-    }
-    if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
-    {
-        i64 want = (s.T * s.B + 7) / 8;
-        int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
-        k_expand<<<grid, 256, 0, st>>>(a);
-        COUNT_LAUNCH(1);
+        if (g > 0) {
+            CUDA_OK(cudaEventRecord(pool->join[g], gs));
+            CUDA_OK(cudaStreamWaitEvent(st, pool->join[g], 0));
+        }
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[4], st));
     if (loss2) {

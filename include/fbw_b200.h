@@ -53,6 +53,8 @@ enum {
     FBW_B200_ERR_SEQ_TOO_LARGE  = 32  /* a sequence has more than 65535 states or classes */
 };
 
+#define FBW_B200_GROUPS 8
+
 /* Sizes the host needs after fbw_b200_prepare (HOST struct). */
 typedef struct fbw_b200_summary {
     int64_t error;        /* validation bits above; 0 = automata accepted                         */
@@ -64,7 +66,11 @@ typedef struct fbw_b200_summary {
     int64_t max_states, max_edges, max_slots, max_len; /* per-sequence maxima                    */
     int64_t sum_len;      /* sum over sequences of valid frames                                   */
     int64_t gather_units, post_units; /* work items of the gather / posterior kernels             */
-    int64_t reserved[4];
+    /* Sequences are ranked by cost (frames x edges, descending); group g is the rank range
+     * [g*B/FBW_B200_GROUPS, (g+1)*B/FBW_B200_GROUPS).  Per-group maxima size each group's launch. */
+    int64_t group_max_states[8], group_max_edges[8], group_max_slots[8];
+    int64_t max_degree;   /* largest in-degree or out-degree of a state                           */
+    int64_t reserved[3];
 } fbw_b200_summary;
 
 /* Bytes of plan scratch for B sequences, E edges, S states. */
