@@ -6,13 +6,16 @@
 // (5T+7 launches); this file sorts the automata once per call and then runs five kernels:
 //
 //   prepare   : validate, number states per sequence, sort edges by target state (forward list),
-//               by source state (backward list), by (sequence, emission) and by sequence.
+//               by source state (backward list), by (sequence, emission) and by sequence; rank the
+//               sequences by cost.
 //   k_gather  : am_scores[t,b,emission] for the distinct emissions of each sequence -> compact
-//               score arrays (frame-major for the sweeps, 32-frame tiles for the posterior pass).
-//   k_sweep   : one persistent CTA per (sequence, direction); the automaton lives in shared memory,
-//               frames are stepped with one barrier each, next frames' scores arrive by cp.async.
-//   k_post    : time-parallel; one warp per (sequence, 32 frames), lane = frame.  Edge scores,
-//               the per-frame normaliser and the per-class posteriors.
+//               score arrays (frame-major for the sweeps, 32-frame tiles for the score pass).
+//   k_sweep   : one persistent CTA per (sequence, direction); the automaton lives in shared memory
+//               and registers, frames are stepped with one barrier each, next frames' scores arrive
+//               by cp.async; state scores leave as full 128-byte lines of a tiled layout.
+//   k_score   : time-parallel; edge scores of every (frame, edge), lane = frame.
+//   k_norm    : per (sequence, 32 frames): the frame normaliser, a serial left fold.
+//   k_class   : per (sequence, 32 frames): the class posteriors.
 //   k_expand  : streams the (T,B,F) output: +inf rows with the few finite posteriors patched in.
 //
 // Arithmetic is kept in the reference's fp32 operation order wherever that order is deterministic
@@ -58,6 +61,8 @@ struct PlanLayout {
     size_t seq_T, start_l, end_l;                                                // int[B]
     size_t ta_off, tg_off, gf_off, gu_off, pu_off;                               // i64[B+1]
     size_t order, cost;                                                          // int[B], i64[B]
+    size_t tx_off;                                                               // i64[B+1]
+    size_t qpos, m_pos;                                                          // int[E], int2[E]
     size_t eiota, keyq, keyf, keyb, key32_out, qe, fe, be, me, slot_of_edge;     // [E]
     size_t key64, key64_out;                                                     // u64[E]
     size_t head, hs, m_ptr;                                                      // int[E+1]
@@ -116,6 +121,9 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.pu_off       = take(8 * (nB + 1));
     L.order        = take(4 * nB);
     L.cost         = take(8 * nB);
+    L.tx_off       = take(8 * (nB + 1));
+    L.qpos         = take(4 * nE);
+    L.m_pos        = take(8 * nE);
     L.eiota        = take(4 * nE);
     L.keyq         = take(4 * nE);
     L.keyf         = take(4 * nE);
@@ -362,12 +370,13 @@ __global__ void k_heads(const unsigned long long* __restrict__ key64s, i64 E, in
 
 // hs[i] = number of class-group heads before position i of the (sequence, emission)-sorted list
 __global__ void k_slots(const unsigned long long* __restrict__ key64s, const int* __restrict__ me,
-                        const int* __restrict__ head, const int* __restrict__ hs, i64 E, i64 F,
-                        int* slot_of_edge, int* slot_emis, int* m_ptr,
-                        const fbw_b200_summary* hdr) {
+                        const int* __restrict__ qe, const int* __restrict__ head,
+                        const int* __restrict__ hs, i64 E, i64 F, int* slot_of_edge, int* slot_emis,
+                        int* m_ptr, int* qpos, const fbw_b200_summary* hdr) {
     if (hdr->error) return;
     i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < E) {
+        qpos[qe[i]] = (int)i;  // position of an edge in the sequence-grouped ascending list
         int g = hs[i] + head[i] - 1;  // global slot of this edge
         if (head[i]) {
             slot_emis[g] = (int)(key64s[i] % (unsigned long long)F);
@@ -391,14 +400,14 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
                                               const int* __restrict__ packed_of, int B, i64 T,
                                               i64 F, i64 E, i64 S, int* slot_off, int* start_l,
                                               int* end_l, i64* ta_off, i64* tg_off, i64* gf_off,
-                                              i64* gu_off, i64* pu_off, i64* cost, int* order,
-                                              fbw_b200_summary* hdr) {
+                                              i64* gu_off, i64* pu_off, i64* tx_off, i64* cost,
+                                              int* order, fbw_b200_summary* hdr) {
     typedef cub::BlockScan<i64, 1024> Scan;
     __shared__ typename Scan::TempStorage tmp;
-    __shared__ i64 carry[6];
+    __shared__ i64 carry[8];
     __shared__ int smax[4];
     __shared__ int gmax[3][FBW_B200_GROUPS];
-    if (threadIdx.x < 6) carry[threadIdx.x] = 0;
+    if (threadIdx.x < 8) carry[threadIdx.x] = 0;
     if (threadIdx.x < 4) smax[threadIdx.x] = 0;
     if (threadIdx.x < 3 * FBW_B200_GROUPS) (&gmax[0][0])[threadIdx.x] = 0;
     __syncthreads();
@@ -407,7 +416,7 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
     for (int base = 0; base < B; base += 1024) {
         int  b  = base + threadIdx.x;
         bool ok = b < B;
-        i64  v[4] = {0, 0, 0, 0};
+        i64  v[5] = {0, 0, 0, 0, 0};
         if (ok) {
             int Sb = state_off[b + 1] - state_off[b];
             int Eb = edge_off[b + 1] - edge_off[b];
@@ -425,17 +434,18 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
             v[1] = (i64)nt * Db * kTile;
             v[2] = (i64)Te * Dp;
             v[3] = Te;
+            v[4] = (i64)nt * Eb * kTile;
             cost[b] = (i64)Te * (Eb + 1);
             atomicMax(&smax[0], Sb);
             atomicMax(&smax[1], Eb);
             atomicMax(&smax[2], Db);
             atomicMax(&smax[3], Te);
         }
-        i64* dst[3] = {ta_off, tg_off, gf_off};
-        for (int k = 0; k < 4; k++) {
+        i64* dst[5] = {ta_off, tg_off, gf_off, nullptr, tx_off};
+        for (int k = 0; k < 5; k++) {
             i64 ex, agg;
             Scan(tmp).ExclusiveSum(v[k], ex, agg);
-            if (ok && k < 3) dst[k][b] = carry[k] + ex;
+            if (ok && dst[k]) dst[k][b] = carry[k] + ex;
             __syncthreads();
             if (threadIdx.x == 0) carry[k] += agg;
             __syncthreads();
@@ -477,9 +487,9 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         for (int k = 0; k < 2; k++) {
             i64 ex, agg;
             Scan(tmp).ExclusiveSum(v[k], ex, agg);
-            if (ok) dst[k][r] = carry[4 + k] + ex;
+            if (ok) dst[k][r] = carry[5 + k] + ex;
             __syncthreads();
-            if (threadIdx.x == 0) carry[4 + k] += agg;
+            if (threadIdx.x == 0) carry[5 + k] += agg;
             __syncthreads();
         }
     }
@@ -487,15 +497,17 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         ta_off[B] = carry[0];
         tg_off[B] = carry[1];
         gf_off[B] = carry[2];
-        gu_off[B] = carry[4];
-        pu_off[B] = carry[5];
+        gu_off[B] = carry[5];
+        pu_off[B] = carry[6];
+        tx_off[B] = carry[4];
+        hdr->score_floats = carry[4];
         hdr->T = T; hdr->B = B; hdr->F = F; hdr->E = E; hdr->S = S;
         hdr->state_floats = carry[0];
         hdr->tiled_floats = carry[1];
         hdr->frame_floats = carry[2];
         hdr->sum_len      = carry[3];
-        hdr->gather_units = carry[4];
-        hdr->post_units   = carry[5];
+        hdr->gather_units = carry[5];
+        hdr->post_units   = carry[6];
         hdr->num_slots    = hs[E];
         hdr->max_states = smax[0];
         hdr->max_edges  = smax[1];
@@ -517,8 +529,9 @@ __global__ void k_records(const int* __restrict__ edges, const float* __restrict
                           const int* __restrict__ packed_of, const int* __restrict__ state_off,
                           const int* __restrict__ slot_off, const int* __restrict__ slot_of_edge,
                           const int* __restrict__ qe, const int* __restrict__ fe,
-                          const int* __restrict__ be, const int* __restrict__ me, uint2* fwd_rec,
-                          uint2* bwd_rec, int4* q_rec, int4* m_rec,
+                          const int* __restrict__ be, const int* __restrict__ me,
+                          const int* __restrict__ qpos, const int* __restrict__ edge_off,
+                          uint2* fwd_rec, uint2* bwd_rec, int4* q_rec, int4* m_rec, int2* m_pos,
                           const fbw_b200_summary* hdr) {
     if (hdr->error) return;
     i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
@@ -540,6 +553,8 @@ __global__ void k_records(const int* __restrict__ edges, const float* __restrict
     q_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
     rec(me[i], fr, to, sl, w);
     m_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
+    // (position in the sequence's ascending edge list, slot) for the class-posterior pass
+    m_pos[i] = make_int2(qpos[me[i]] - edge_off[edges[3 * E + me[i]]], sl);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -550,10 +565,11 @@ struct RunArgs {
     float*       out;
     float*       sums;
     float*       loss2;
-    float *A, *Bt, *Gt, *Gf, *P;
+    float *A, *Bt, *Gt, *Gf, *P, *X, *N;
     int* status;  // device status word of the call (0 = ok)
     const int *state_off, *edge_off, *slot_off, *seq_T, *start_l, *end_l;
-    const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off;
+    const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off, *tx_off;
+    const int2* m_pos;
     const int *rowptr_f, *rowptr_b;
     const uint2 *fwd_rec, *bwd_rec;
     const int4 *q_rec, *m_rec;
@@ -836,62 +852,53 @@ __device__ __forceinline__ void named_arrive(int count) {
     asm volatile("bar.arrive %0, %1;" ::"n"(ID), "r"(count) : "memory");
 }
 
-constexpr int kPostEdges = 40;  // edges per chunk of the normaliser fold (5 batches)
-constexpr int kPostBatch = 8;   // edges whose lines are loaded together
-struct __align__(16) PostSmem {
-    float x[2][kPostEdges][kTile];        // edge scores, [buffer][edge][frame]
-    float stage[2][kTile][kTile + 1];     // per-warp posterior transpose
-    float acc[kTile];                     // the frame normalisers, handed from warp 0 to warp 1
+constexpr int kPostBatch = 8;  // edges whose lines are loaded together
+
+// decode a work unit (sequence, 32-frame tile) from its index in rank order
+struct PostUnit {
+    int b, k, Sb, e0, Eb, so, Db, Dp, Te;
+    i64 u;
 };
+__device__ __forceinline__ PostUnit post_unit(const RunArgs& a, i64 u) {
+    PostUnit p;
+    const int rk = find_seq(a.pu_off, (int)a.B, u);
+    p.u  = u;
+    p.b  = a.order[rk];
+    p.k  = (int)(u - a.pu_off[rk]);
+    p.Sb = a.state_off[p.b + 1] - a.state_off[p.b];
+    p.e0 = a.edge_off[p.b];
+    p.Eb = a.edge_off[p.b + 1] - p.e0;
+    p.so = a.slot_off[p.b];
+    p.Db = a.slot_off[p.b + 1] - p.so;
+    p.Dp = (p.Db + 3) & ~3;
+    p.Te = a.seq_T[p.b];
+    return p;
+}
 
-// Edge scores, normaliser and class posteriors; one CTA of two warps per (sequence, 32-frame tile),
-// lane = frame.  For frame t:
-//   x_e  = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)              (fbw_op.cu:93-100)
-//   sum  = left fold of prob_add over the sequence's edges in ascending edge index (fbw_op.cu:115-118)
-//   sums[t,b] = isinf(sum) ? 0 : sum                                              (fbw_op.cu:120-129)
-//   post[t][slot] = -log sum over the slot's edges of exp(-(x_e - sum))           (fbw_op.cu:131-153)
-// In the tiled layouts the 32 frames of one state (or slot) are one 128-byte line, so every load of a
-// warp is one line.  The fold is the only serial part: warp 1 computes the edge scores 32 edges
-// ahead into a double buffer in shared memory, warp 0 only folds them (steps whose result is
-// provably the running minimum in every lane skip expf/log1pf).  The class posteriors are then
-// split between both warps by blocks of 32 slots.
-__global__ void __launch_bounds__(64, 10) k_post(RunArgs a) {
-    __shared__ PostSmem sm;
+// Edge scores of every (frame, edge):
+//   x_e = ((alpha_t(from) + w) + score_t(emission)) + beta_{t+1}(to)              (fbw_op.cu:93-100)
+// written as X[tile][edge in ascending edge index][frame].  An unreachable source or target state
+// has score +inf and so has the sum, which is what the reference stores for such an edge
+// (fbw_op.cu:82-85).  One CTA per (sequence, 32-frame tile), lane = frame; in the tiled layouts
+// every load and store of a warp is one 128-byte line.  Fully parallel: no fold here.
+__global__ void __launch_bounds__(256) k_score(RunArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int B = (int)a.B;
-
-    // Units are in descending cost order.  CTA w takes units w, 2W-1-w, 2W+w, 4W-1-w, ...: a CTA
-    // that drew an expensive unit in one round draws a cheap one in the next.
     const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
-    const i64 W = gridDim.x, w = blockIdx.x;
-    for (i64 round = 0; round * W < nunits; round++) {
-        const i64 idx = (round & 1) ? (round + 1) * W - 1 - w : round * W + w;
-        if (idx >= nunits) continue;  // uniform in the CTA
-        const i64 u  = u0 + idx;
-        const int rk = find_seq(a.pu_off, B, u);
-        const int b  = a.order[rk];
-        const int k  = (int)(u - a.pu_off[rk]);
-        const int Sb = a.state_off[b + 1] - a.state_off[b];
-        const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
-        const int so = a.slot_off[b], Db = a.slot_off[b + 1] - so;
-        const int Dp = (Db + 3) & ~3;
-        const int Te = a.seq_T[b];
-        const int t  = k * kTile + lane;
-        const bool valid = t < Te;
-        // every lane loads (the tile is allocated for all 32 frames); lanes past the sequence's
-        // length read unspecified values and are forced to +inf
-        const float* __restrict__ Ab = a.A + a.ta_off[b] + (i64)k * Sb * kTile + lane;
-        const float* __restrict__ Bb = a.Bt + a.ta_off[b] + (i64)k * Sb * kTile + lane;
-        const float* __restrict__ Gb = a.Gt + a.tg_off[b] + (i64)k * Db * kTile + lane;
-
-        // scores of edges recs[i0 .. i0+kPostBatch): all loads first (straight-line, so they are in
-        // flight together), then the arithmetic.  The reference writes +inf for an edge whose
-        // source (forward) or target (backward) state is unreachable (fbw_op.cu:82-85).
-        auto batch_scores = [&](const int4* __restrict__ recs, int i0, int iend, float* x, int* sl) {
+    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        const bool valid = p.k * kTile + lane < p.Te;
+        // every lane loads (a tile is allocated for all 32 frames); frames past the sequence's
+        // length hold unspecified values and get +inf
+        const float* __restrict__ Ab = a.A + a.ta_off[p.b] + (i64)p.k * p.Sb * kTile + lane;
+        const float* __restrict__ Bb = a.Bt + a.ta_off[p.b] + (i64)p.k * p.Sb * kTile + lane;
+        const float* __restrict__ Gb = a.Gt + a.tg_off[p.b] + (i64)p.k * p.Db * kTile + lane;
+        float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
+        const int4* __restrict__ q = a.q_rec + p.e0;
+        for (int i0 = warp * kPostBatch; i0 < p.Eb; i0 += 8 * kPostBatch) {
             int4  r[kPostBatch];
             float al[kPostBatch], be[kPostBatch], g[kPostBatch];
 #pragma unroll
-            for (int j = 0; j < kPostBatch; j++) r[j] = __ldg(recs + min(i0 + j, iend - 1));
+            for (int j = 0; j < kPostBatch; j++) r[j] = __ldg(q + min(i0 + j, p.Eb - 1));
 #pragma unroll
             for (int j = 0; j < kPostBatch; j++) {
                 al[j] = Ab[r[j].x * kTile];
@@ -900,79 +907,91 @@ __global__ void __launch_bounds__(64, 10) k_post(RunArgs a) {
             }
 #pragma unroll
             for (int j = 0; j < kPostBatch; j++) {
-                // an unreachable source or target state has score +inf and the sum is +inf, which
-                // is what the reference stores for such an edge (fbw_op.cu:82-85)
                 const float v = ((al[j] + __int_as_float(r[j].w)) + g[j]) + be[j];
-                x[j]  = (!valid || i0 + j >= iend) ? CUDART_INF_F : v;
-                sl[j] = i0 + j < iend ? r[j].z : -1;
+                if (i0 + j < p.Eb) Xb[(i64)(i0 + j) * kTile] = valid ? v : CUDART_INF_F;
             }
-        };
+        }
+    }
+}
 
-        // ---- normaliser ------------------------------------------------------------------------
-        // Both warps compute the edge scores of a chunk into shared memory (warp 0 two batches,
-        // warp 1 three); after the barrier warp 0 folds the chunk in ascending edge index while
-        // warp 1 already loads the next one.  One barrier per chunk orders everything: a buffer is
-        // rewritten two chunks later, after a barrier that warp 0 reaches only when its fold is done.
-        const int4* __restrict__ q = a.q_rec + e0;
-        const int nchunks = (Eb + kPostEdges - 1) / kPostEdges;
-        float facc = CUDART_INF_F;
-        for (int c = 0; c < nchunks; c++) {
-            const int i0 = c * kPostEdges, i1 = min(i0 + kPostEdges, Eb);
-            const int b_lo = warp == 0 ? 0 : 2, b_hi = warp == 0 ? 2 : kPostEdges / kPostBatch;
-            for (int bb = b_lo; bb < b_hi; bb++) {
-                const int i = i0 + bb * kPostBatch;
-                if (i >= i1) break;
-                float x[kPostBatch];
-                int   sl[kPostBatch];
-                batch_scores(q, i, i1, x, sl);
+// Frame normalisers: sum = left fold of prob_add over the sequence's edges in ascending edge index
+// (fbw_op.cu:115-118), sums[t,b] = isinf(sum) ? 0 : sum (fbw_op.cu:120-129).  One warp per
+// (sequence, 32-frame tile), lane = frame, streaming the tile's edge scores in storage order; the
+// next 8 lines are loaded while the current 8 are folded.  Steps whose result is provably the
+// running minimum skip expf/log1pf (exact).  The raw sum (+inf for a dead frame) goes to N.
+// Every unit is its own warp so that all the serial folds of a call run side by side.
+__global__ void __launch_bounds__(128) k_norm(RunArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    const i64 W = (i64)gridDim.x * 4;
+    for (i64 idx = (i64)blockIdx.x * 4 + warp; idx < nunits; idx += W) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        const int  t     = p.k * kTile + lane;
+        const bool valid = t < p.Te;
+        const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
+        float acc = CUDART_INF_F;
+        float nx[kPostBatch];
 #pragma unroll
-                for (int j = 0; j < kPostBatch; j++) {
-                    if (i + j < i1) sm.x[c & 1][i - i0 + j][lane] = x[j];
-                }
+        for (int j = 0; j < kPostBatch; j++) nx[j] = j < p.Eb ? Xb[(i64)j * kTile] : CUDART_INF_F;
+        for (int i0 = 0; i0 < p.Eb; i0 += kPostBatch) {
+            float x[kPostBatch];
+#pragma unroll
+            for (int j = 0; j < kPostBatch; j++) x[j] = nx[j];
+#pragma unroll
+            for (int j = 0; j < kPostBatch; j++) {
+                const int i = i0 + kPostBatch + j;
+                nx[j] = i < p.Eb ? Xb[(i64)i * kTile] : CUDART_INF_F;
             }
-            __syncthreads();
-            if (warp == 0) {
-                const int ne = i1 - i0;
-                for (int j = 0; j < ne; j++) facc = prob_add_fast(facc, sm.x[c & 1][j][lane]);
-            }
+#pragma unroll
+            for (int j = 0; j < kPostBatch; j++) acc = prob_add_fast(acc, x[j]);
         }
-        if (warp == 0) {
-            if (valid) a.sums[(i64)t * B + b] = isinf(facc) ? 0.f : facc;
-            sm.acc[lane] = facc;
-        }
-        __syncthreads();
-        const float acc = sm.acc[lane];
+        if (valid) a.sums[(i64)t * a.B + p.b] = isinf(acc) ? 0.f : acc;
+        a.N[p.u * kTile + lane] = acc;
+    }
+}
 
-        // ---- class posteriors: blocks of 32 slots alternate between the two warps ----------------
-        // Per slot: -log sum_e exp(-(x_e - sum)) as a running (minimum, scaled sum) pair.  The terms
-        // are normalised (magnitude of a log-posterior), so a fast exponential is accurate to ~1e-7
-        // in the posterior; the reference accumulates the same terms with atomics in no fixed order
-        // (fbw_op.cu:137-153).  A slot with one edge gets x_e - sum exactly.
-        const int4* __restrict__ m  = a.m_rec + e0;
-        const int* __restrict__ mp  = a.m_ptr + so;
-        float* __restrict__ Pb      = a.P + a.gf_off[b];
-        float (*st)[kTile + 1]      = sm.stage[warp];
+// Class posteriors: post[t][slot] = -log sum over the slot's edges of exp(-(x_e - sum))
+// (fbw_op.cu:131-153), as a running (minimum, scaled sum) pair.  The terms are normalised
+// (magnitude of a log-posterior), so a fast exponential is accurate to ~1e-7 in the posterior; the
+// reference accumulates the same terms with atomics in no fixed order.  A slot with one edge gets
+// x_e - sum exactly.  One CTA per (sequence, 32-frame tile); each warp takes blocks of 32 slots,
+// lane = frame, and writes them out transposed so that every frame's row of P is contiguous.
+__global__ void __launch_bounds__(128) k_class(RunArgs a) {
+    __shared__ float stage[4][kTile][kTile + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float (*st)[kTile + 1] = stage[warp];
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        const float acc = a.N[p.u * kTile + lane];
         const bool rowdead = !(acc < CUDART_INF_F);  // no path through this frame
-        const int  mbase   = mp[0];                  // position of the sequence's first edge
-        for (int d0 = warp * kTile; d0 < Db; d0 += 2 * kTile) {
-            const int nd = min(kTile, Db - d0);
+        const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
+        const int2* __restrict__ m  = a.m_pos + p.e0;
+        const int* __restrict__ mp  = a.m_ptr + p.so;
+        float* __restrict__ Pb      = a.P + a.gf_off[p.b];
+        const int mbase = mp[0];
+        for (int d0 = warp * kTile; d0 < p.Db; d0 += 4 * kTile) {
+            const int nd = min(kTile, p.Db - d0);
             const int j0 = mp[d0] - mbase, j1 = mp[d0 + nd] - mbase;
             int   cur = -1;
             float mn = CUDART_INF_F, sme = 1.f;
             for (int i = j0; i < j1; i += kPostBatch) {
+                int2  r[kPostBatch];
                 float x[kPostBatch];
-                int   sl[kPostBatch];
-                batch_scores(m, i, j1, x, sl);
+#pragma unroll
+                for (int j = 0; j < kPostBatch; j++) r[j] = __ldg(m + min(i + j, j1 - 1));
+#pragma unroll
+                for (int j = 0; j < kPostBatch; j++) x[j] = Xb[(i64)r[j].x * kTile];
 #pragma unroll
                 for (int j = 0; j < kPostBatch; j++) {
-                    if (sl[j] < 0) continue;  // past the end of the block (uniform)
+                    if (i + j >= j1) continue;   // past the end of the block (uniform)
                     const float y = x[j] - acc;  // +inf for dead edges; NaN only if the row is dead
-                    if (sl[j] != cur) {          // uniform: a new slot starts
+                    if (r[j].y != cur) {         // uniform: a new slot starts
                         if (cur >= 0) {
                             st[cur - d0][lane] =
                                 (mn == CUDART_INF_F || rowdead) ? CUDART_INF_F : mn - logf(sme);
                         }
-                        cur = sl[j];
+                        cur = r[j].y;
                         mn  = y;
                         sme = 1.f;
                     } else if (y < CUDART_INF_F) {
@@ -991,12 +1010,11 @@ __global__ void __launch_bounds__(64, 10) k_post(RunArgs a) {
             __syncwarp();
             // transpose: frame r of the tile gets its nd posteriors as one contiguous write
             for (int r = 0; r < kTile; r++) {
-                const int tr = k * kTile + r;
-                if (tr < Te && lane < nd) Pb[(i64)tr * Dp + d0 + lane] = st[lane][r];
+                const int tr = p.k * kTile + r;
+                if (tr < p.Te && lane < nd) Pb[(i64)tr * p.Dp + d0 + lane] = st[lane][r];
             }
             __syncwarp();
         }
-        __syncthreads();  // sm.x / sm.acc are reused by the next unit
     }
 }
 
@@ -1109,7 +1127,7 @@ __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i
 // host side
 // ---------------------------------------------------------------------------------------------
 struct RunLayout {
-    size_t status, A, Bt, Gt, Gf, P, total;
+    size_t status, A, Bt, Gt, Gf, P, X, N, total;
 };
 
 RunLayout run_layout(const fbw_b200_summary& s) {
@@ -1126,6 +1144,8 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     L.Gt    = take((size_t)s.tiled_floats);
     L.Gf    = take((size_t)s.frame_floats);
     L.P     = take((size_t)s.frame_floats);
+    L.X     = take((size_t)s.score_floats);
+    L.N     = take((size_t)s.post_units * kTile);
     L.total = off;
     return L;
 }
@@ -1212,7 +1232,6 @@ int choose_groups(const fbw_b200_summary& s) {
     }
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
     const double cells = (double)s.T * (double)s.B * (double)s.F;
-    if (s.B >= 32 && cells >= 2.5e8) return 8;
     if (s.B >= 16 && cells >= 1.0e8) return 4;
     return 1;
 }
@@ -1285,20 +1304,15 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
     if (s.post_units > 0) {
-        // two-warp CTAs, one unit at a time each; all resident at once where possible.  The kernel
-        // needs the large shared-memory carveout to reach ten CTAs per SM.
-        static bool carve_set[64] = {false};
-        int dev = 0;
-        CUDA_OK(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !carve_set[dev]) {
-            CUDA_OK(cudaFuncSetAttribute(k_post, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
-            if (dev >= 0 && dev < 64) carve_set[dev] = true;
-        }
-        i64 want = tiles * nb;
-        int grid = (int)(want < (i64)sms * 12 ? want : (i64)sms * 12);
-        k_post<<<grid > 0 ? grid : 1, 64, 0, st>>>(a);
-        COUNT_LAUNCH(1);
+        const i64 units = tiles * nb;  // upper bound; the kernels read the exact count
+        int g1 = (int)(units < (i64)sms * 8 ? units : (i64)sms * 8);
+        k_score<<<g1 > 0 ? g1 : 1, 256, 0, st>>>(a);
+        i64 w2 = (units + 3) / 4;
+        int g2 = (int)(w2 < (i64)sms * 16 ? w2 : (i64)sms * 16);
+        k_norm<<<g2 > 0 ? g2 : 1, 128, 0, st>>>(a);
+        int g3 = (int)(units < (i64)sms * 12 ? units : (i64)sms * 12);
+        k_class<<<g3 > 0 ? g3 : 1, 128, 0, st>>>(a);
+        COUNT_LAUNCH(3);
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
     {
@@ -1408,11 +1422,11 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
         CUDA_OK(cub::DeviceScan::ExclusiveSum(ctemp, cbytes, at<int>(plan, L.head),
                                               at<int>(plan, L.hs), (int)(E + 1), st));
         k_slots<<<blocks(E + 1), TB, 0, st>>>(at<unsigned long long>(plan, L.key64_out),
-                                              at<int>(plan, L.me), at<int>(plan, L.head),
-                                              at<int>(plan, L.hs), E, F,
+                                              at<int>(plan, L.me), at<int>(plan, L.qe),
+                                              at<int>(plan, L.head), at<int>(plan, L.hs), E, F,
                                               at<int>(plan, L.slot_of_edge),
                                               at<int>(plan, L.slot_emis), at<int>(plan, L.m_ptr),
-                                              hdr);
+                                              at<int>(plan, L.qpos), hdr);
     } else {
         CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowptr_f), 0, 4 * (size_t)(S + 1), st));
         CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowptr_b), 0, 4 * (size_t)(S + 1), st));
@@ -1424,14 +1438,15 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
                                at<int>(plan, L.end_l), at<i64>(plan, L.ta_off),
                                at<i64>(plan, L.tg_off), at<i64>(plan, L.gf_off),
                                at<i64>(plan, L.gu_off), at<i64>(plan, L.pu_off),
-                               at<i64>(plan, L.cost), at<int>(plan, L.order), hdr);
+                               at<i64>(plan, L.tx_off), at<i64>(plan, L.cost),
+                               at<int>(plan, L.order), hdr);
     if (E > 0) {
         k_records<<<blocks(E), TB, 0, st>>>(
             edges, weights, E, at<int>(plan, L.packed_of), at<int>(plan, L.state_off),
             at<int>(plan, L.slot_off), at<int>(plan, L.slot_of_edge), at<int>(plan, L.qe),
-            at<int>(plan, L.fe), at<int>(plan, L.be), at<int>(plan, L.me),
-            at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec), at<int4>(plan, L.q_rec),
-            at<int4>(plan, L.m_rec), hdr);
+            at<int>(plan, L.fe), at<int>(plan, L.be), at<int>(plan, L.me), at<int>(plan, L.qpos),
+            at<int>(plan, L.edge_off), at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec),
+            at<int4>(plan, L.q_rec), at<int4>(plan, L.m_rec), at<int2>(plan, L.m_pos), hdr);
     }
     CUDA_OK(cudaGetLastError());
     return FBW_B200_OK;
@@ -1469,6 +1484,8 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.Gt = at<float>(work, R.Gt);
     a.Gf = at<float>(work, R.Gf);
     a.P  = at<float>(work, R.P);
+    a.X  = at<float>(work, R.X);
+    a.N  = at<float>(work, R.N);
     a.status = at<int>(work, R.status);
     a.state_off = at<int>(plan, L.state_off);
     a.edge_off  = at<int>(plan, L.edge_off);
@@ -1481,6 +1498,8 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.gf_off = at<i64>(plan, L.gf_off);
     a.gu_off = at<i64>(plan, L.gu_off);
     a.pu_off = at<i64>(plan, L.pu_off);
+    a.tx_off = at<i64>(plan, L.tx_off);
+    a.m_pos  = at<int2>(plan, L.m_pos);
     a.rowptr_f = at<int>(plan, L.rowptr_f);
     a.rowptr_b = at<int>(plan, L.rowptr_b);
     a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
@@ -1498,9 +1517,9 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
 
     // Sequence groups (rank ranges of similar cost) run as independent pipelines
-    // gather -> sweep -> posterior -> expand on their own streams: the sweeps of cheap groups end
-    // early and their memory-bound output pass overlaps the arithmetic-bound sweep of the
-    // expensive ones.  With phase events everything runs as one group on the caller's stream.
+    // gather -> sweep -> scores -> posteriors -> expand on their own streams, so that one group's
+    // arithmetic-bound posterior pass overlaps another's memory-bound output pass.  With phase
+    // events everything runs as one group on the caller's stream.
     int G = ev ? 1 : choose_groups(s);
     StreamPool* pool = nullptr;
     std::unique_lock<std::mutex> lock;
