@@ -956,7 +956,7 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
 // reference accumulates the same terms with atomics in no fixed order.  A slot with one edge gets
 // x_e - sum exactly.  One CTA per (sequence, 32-frame tile); each warp takes blocks of 32 slots,
 // lane = frame, and writes them out transposed so that every frame's row of P is contiguous.
-__global__ void __launch_bounds__(128) k_class(RunArgs a) {
+__global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
     __shared__ float stage[4][kTile][kTile + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float (*st)[kTile + 1] = stage[warp];

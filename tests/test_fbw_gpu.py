@@ -292,7 +292,18 @@ def test_full_size_triphone_properties(fbw_mod, ref_core, cuda):
         rec["post_vs_ref"] = post_abs_diff(out, r_out)
         rec["bit_identical_sums"] = bool(torch.equal(sums, r_sums))
         del out
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         r_out2, _ = run_ref(ref_core, am, b, cuda)
+        e1.record()
+        torch.cuda.synchronize()
+        rec["ref_op_ms"] = e0.elapsed_time(e1)  # the reference's own GPU op on the same device
+        e0.record()
+        o3 = fbw_mod.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, fsa[0], fbw_mod.core.DebugOptions())
+        e1.record()
+        torch.cuda.synchronize()
+        rec["new_op_ms"] = e0.elapsed_time(e1)
+        del o3
         rec["ref_vs_ref_post"] = post_abs_diff(r_out, r_out2)
         report("triphone_full", **rec)
         assert rec["loss_vs_ref"] <= LOSS_RTOL
