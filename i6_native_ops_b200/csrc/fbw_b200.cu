@@ -58,7 +58,7 @@ struct PlanLayout {
     size_t header;
     size_t state_key, skey, skey_out, siota, sorted_state, packed_of;            // [S]
     size_t scount, ecount, state_off, edge_off, slot_off;                        // int[B+1]
-    size_t seq_T, start_l, end_l;                                                // int[B]
+    size_t seq_T, start_l, end_l, nslot;                                         // int[B]
     size_t ta_off, tg_off, gf_off, gu_off, pu_off;                               // i64[B+1]
     size_t order, cost;                                                          // int[B], i64[B]
     size_t tx_off;                                                               // i64[B+1]
@@ -114,6 +114,7 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.seq_T        = take(4 * nB);
     L.start_l      = take(4 * nB);
     L.end_l        = take(4 * nB);
+    L.nslot        = take(4 * nB);
     L.ta_off       = take(8 * (nB + 1));
     L.tg_off       = take(8 * (nB + 1));
     L.gf_off       = take(8 * (nB + 1));
@@ -138,7 +139,7 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.key64_out    = take(8 * nE);
     L.head         = take(4 * (nE + 1));
     L.hs           = take(4 * (nE + 1));
-    L.m_ptr        = take(4 * (nE + 1));
+    L.m_ptr        = take(4 * (nE + nB + 1));
     L.rowcnt_f     = take(4 * (nS + 1));
     L.rowptr_f     = take(4 * (nS + 1));
     L.rowcnt_b     = take(4 * (nS + 1));
@@ -147,7 +148,7 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.bwd_rec      = take(8 * nE);
     L.q_rec        = take(16 * nE);
     L.m_rec        = take(16 * nE);
-    L.slot_emis    = take(4 * nE);
+    L.slot_emis    = take(4 * (nE + nB + 1));
     L.cub_temp_bytes = cub_temp_need(E, S);
     L.cub_temp       = take(L.cub_temp_bytes);
     L.total          = off;
@@ -269,7 +270,10 @@ __global__ void k_mark(const int* __restrict__ edges, const int* __restrict__ st
             atomicOr((unsigned long long*)&hdr->error, err);
             return;
         }
-        atomicAdd(&ecount[sq], 1);
+        {   // one atomic per group of lanes that share the sequence (edges usually arrive grouped)
+            const unsigned peers = __match_any_sync(__activemask(), sq);
+            if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&ecount[sq], __popc(peers));
+        }
         claim_state(state_key, scount, fr, sq, hdr);
         claim_state(state_key, scount, to, sq, hdr);
     } else if (idx < E + B) {
@@ -398,10 +402,11 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
                                               const int* __restrict__ seq_T,
                                               const int* __restrict__ start_end,
                                               const int* __restrict__ packed_of, int B, i64 T,
-                                              i64 F, i64 E, i64 S, int* slot_off, int* start_l,
+                                              i64 F, i64 E, i64 S, int* slot_off, int* nslot,
+                                              int* start_l,
                                               int* end_l, i64* ta_off, i64* tg_off, i64* gf_off,
                                               i64* gu_off, i64* pu_off, i64* tx_off, i64* cost,
-                                              int* order, fbw_b200_summary* hdr) {
+                                              int* order, int fast, fbw_b200_summary* hdr) {
     typedef cub::BlockScan<i64, 1024> Scan;
     __shared__ typename Scan::TempStorage tmp;
     __shared__ i64 carry[8];
@@ -416,16 +421,19 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
     for (int base = 0; base < B; base += 1024) {
         int  b  = base + threadIdx.x;
         bool ok = b < B;
-        i64  v[5] = {0, 0, 0, 0, 0};
+        i64  v[6] = {0, 0, 0, 0, 0, 0};
         if (ok) {
             int Sb = state_off[b + 1] - state_off[b];
             int Eb = edge_off[b + 1] - edge_off[b];
-            int so = hs[edge_off[b]];
-            int Db = hs[edge_off[b + 1]] - so;
+            // slot base and count: from the head scan (general path) or already written per
+            // sequence by k_seqsort (fast path)
+            int so = fast ? slot_off[b] : hs[edge_off[b]];
+            int Db = fast ? nslot[b] : hs[edge_off[b + 1]] - so;
             int Te = seq_T[b];
             int nt = (Te + kTile - 1) / kTile;
             int Dp = (Db + 3) & ~3;
             slot_off[b] = so;
+            nslot[b]    = Db;
             if (!bad) {
                 start_l[b] = packed_of[start_end[b]] - state_off[b];
                 end_l[b]   = packed_of[start_end[B + b]] - state_off[b];
@@ -435,14 +443,15 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
             v[2] = (i64)Te * Dp;
             v[3] = Te;
             v[4] = (i64)nt * Eb * kTile;
+            v[5] = Db;
             cost[b] = (i64)Te * (Eb + 1);
             atomicMax(&smax[0], Sb);
             atomicMax(&smax[1], Eb);
             atomicMax(&smax[2], Db);
             atomicMax(&smax[3], Te);
         }
-        i64* dst[5] = {ta_off, tg_off, gf_off, nullptr, tx_off};
-        for (int k = 0; k < 5; k++) {
+        i64* dst[6] = {ta_off, tg_off, gf_off, nullptr, tx_off, nullptr};
+        for (int k = 0; k < 6; k++) {
             i64 ex, agg;
             Scan(tmp).ExclusiveSum(v[k], ex, agg);
             if (ok && dst[k]) dst[k][b] = carry[k] + ex;
@@ -451,7 +460,7 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
             __syncthreads();
         }
     }
-    if (threadIdx.x == 0) slot_off[B] = hs[E];
+    if (threadIdx.x == 0 && !fast) slot_off[B] = hs[E];
     __syncthreads();
     // ---- rank by descending cost (ties: ascending sequence id) ----
     for (int b = threadIdx.x; b < B; b += 1024) {
@@ -471,7 +480,7 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         i64  v[2] = {0, 0};
         if (ok) {
             int b  = order[r];
-            int Db = slot_off[b + 1] - slot_off[b];
+            int Db = nslot[b];
             int nt = (seq_T[b] + kTile - 1) / kTile;
             v[0] = (i64)nt * ((Db + kGatherSlots - 1) / kGatherSlots);
             v[1] = nt;
@@ -487,9 +496,9 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         for (int k = 0; k < 2; k++) {
             i64 ex, agg;
             Scan(tmp).ExclusiveSum(v[k], ex, agg);
-            if (ok) dst[k][r] = carry[5 + k] + ex;
+            if (ok) dst[k][r] = carry[6 + k] + ex;
             __syncthreads();
-            if (threadIdx.x == 0) carry[5 + k] += agg;
+            if (threadIdx.x == 0) carry[6 + k] += agg;
             __syncthreads();
         }
     }
@@ -497,8 +506,8 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         ta_off[B] = carry[0];
         tg_off[B] = carry[1];
         gf_off[B] = carry[2];
-        gu_off[B] = carry[5];
-        pu_off[B] = carry[6];
+        gu_off[B] = carry[6];
+        pu_off[B] = carry[7];
         tx_off[B] = carry[4];
         hdr->score_floats = carry[4];
         hdr->T = T; hdr->B = B; hdr->F = F; hdr->E = E; hdr->S = S;
@@ -506,9 +515,9 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         hdr->tiled_floats = carry[1];
         hdr->frame_floats = carry[2];
         hdr->sum_len      = carry[3];
-        hdr->gather_units = carry[5];
-        hdr->post_units   = carry[6];
-        hdr->num_slots    = hs[E];
+        hdr->gather_units = carry[6];
+        hdr->post_units   = carry[7];
+        hdr->num_slots    = carry[5];
         hdr->max_states = smax[0];
         hdr->max_edges  = smax[1];
         hdr->max_slots  = smax[2];
@@ -521,6 +530,174 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         if (smax[0] > kMaxPerSeq || smax[2] > kMaxPerSeq) {
             hdr->error |= FBW_B200_ERR_SEQ_TOO_LARGE;
         }
+    }
+}
+
+// ---- fast path of prepare: one CTA sorts one sequence in shared memory --------------------------
+constexpr int kFastThreads = 512;
+constexpr int kFastItems   = 8;
+constexpr int kFastCap     = kFastThreads * kFastItems;  // edges per sequence
+constexpr int kFastPosBits = 12;                         // log2(kFastCap)
+
+__global__ void k_seqkeys(const int* __restrict__ edges, i64 E, unsigned* keyq, int* eiota,
+                          const fbw_b200_summary* hdr) {
+    if (hdr->error) return;
+    i64 e = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < E) {
+        keyq[e]  = (unsigned)edges[3 * E + e];
+        eiota[e] = (int)e;
+    }
+}
+
+typedef cub::BlockRadixSort<unsigned, kFastThreads, kFastItems> FastSort;
+typedef cub::BlockScan<int, kFastThreads>                       FastScan;
+struct FastSmem {
+    union {
+        typename FastSort::TempStorage sort;
+        typename FastScan::TempStorage scan;
+    } t;
+    unsigned sorted[kFastCap];     // the keys of the last sort, in order
+    unsigned short from[kFastCap], to[kFastCap], slot[kFastCap];
+    int      emis[kFastCap];
+    unsigned last[kFastThreads];   // each thread's last sorted key (for the head test)
+    int      deg_max;
+};
+
+// Builds everything the run kernels need for sequence b = blockIdx.x from the sequence-grouped edge
+// list qe (ascending edge index inside the sequence): local slot numbers (distinct emissions in
+// ascending order), the target-sorted and source-sorted edge lists with their row pointers, the
+// emission-sorted list, all stable in edge index because the position in qe is the low part of every
+// sort key.  Three block-wide radix sorts of at most 4096 keys replace three device-wide sorts.
+__global__ void __launch_bounds__(kFastThreads) k_seqsort(
+    const int* __restrict__ edges, const float* __restrict__ weights, i64 E, i64 F,
+    const int* __restrict__ qe, const int* __restrict__ edge_off, const int* __restrict__ state_off,
+    const int* __restrict__ packed_of, int* rowptr_f, int* rowptr_b, uint2* fwd_rec, uint2* bwd_rec,
+    int4* q_rec, int4* m_rec, int2* m_pos, int* m_ptr, int* slot_emis, int* slot_off, int* nslot,
+    fbw_b200_summary* hdr) {
+    extern __shared__ __align__(16) unsigned char fast_raw[];
+    FastSmem& sm = *reinterpret_cast<FastSmem*>(fast_raw);
+    if (hdr->error & ~(i64)FBW_B200_ERR_RETRY_GENERAL) return;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int e0 = edge_off[b], Eb = edge_off[b + 1] - e0;
+    const int s0 = state_off[b], Sb = state_off[b + 1] - s0;
+    const int so = e0 + b;  // base of this sequence's slot arrays (at most Eb slots, plus one end entry)
+    if (tid == 0) slot_off[b] = so;
+    if (Eb > kFastCap || F > (i64)(1u << (32 - kFastPosBits))) {
+        if (tid == 0) {
+            atomicOr((unsigned long long*)&hdr->error, (unsigned long long)FBW_B200_ERR_RETRY_GENERAL);
+            nslot[b] = 0;
+        }
+        return;
+    }
+    if (tid == 0) sm.deg_max = 0;
+    for (int i = tid; i < Eb; i += kFastThreads) {
+        const int e = qe[e0 + i];
+        sm.from[i] = (unsigned short)(packed_of[edges[e]] - s0);
+        sm.to[i]   = (unsigned short)(packed_of[edges[E + e]] - s0);
+        sm.emis[i] = edges[2 * E + e];
+    }
+    __syncthreads();
+    const unsigned pos_mask = (1u << kFastPosBits) - 1u;
+    unsigned keys[kFastItems];
+
+    // ---- slots: sort by (emission, position) ----
+#pragma unroll
+    for (int k = 0; k < kFastItems; k++) {
+        const int i = tid * kFastItems + k;
+        keys[k] = i < Eb ? ((unsigned)sm.emis[i] << kFastPosBits) | (unsigned)i : 0xffffffffu;
+    }
+    FastSort(sm.t.sort).Sort(keys);
+    sm.last[tid] = keys[kFastItems - 1];
+    __syncthreads();
+    int heads = 0;
+    bool head[kFastItems];
+#pragma unroll
+    for (int k = 0; k < kFastItems; k++) {
+        const int j = tid * kFastItems + k;
+        const unsigned prev = k > 0 ? keys[k - 1] : (tid > 0 ? sm.last[tid - 1] : 0xffffffffu);
+        head[k] = j < Eb && (j == 0 || (keys[k] >> kFastPosBits) != (prev >> kFastPosBits));
+        heads += head[k] ? 1 : 0;
+    }
+    int before, total;
+    FastScan(sm.t.scan).ExclusiveSum(heads, before, total);
+    {
+        int slot = before - 1;
+#pragma unroll
+        for (int k = 0; k < kFastItems; k++) {
+            const int j = tid * kFastItems + k;
+            if (j >= Eb) break;
+            if (head[k]) {
+                slot++;
+                slot_emis[so + slot] = (int)(keys[k] >> kFastPosBits);
+                m_ptr[so + slot]     = e0 + j;
+            }
+            const int i = (int)(keys[k] & pos_mask);
+            sm.slot[i] = (unsigned short)slot;
+            m_pos[e0 + j] = make_int2(i, slot);
+            m_rec[e0 + j] = make_int4((int)sm.from[i], (int)sm.to[i], slot,
+                                      __float_as_int(weights[qe[e0 + i]]));
+        }
+    }
+    if (tid == 0) {
+        m_ptr[so + total] = e0 + Eb;
+        nslot[b]          = total;
+    }
+    __syncthreads();
+
+    // ---- forward list (by target state) and backward list (by source state) ----
+    for (int dir = 0; dir < 2; dir++) {
+        const unsigned short* key_state = dir == 0 ? sm.to : sm.from;
+        const unsigned short* other     = dir == 0 ? sm.from : sm.to;
+        int*   rowptr = dir == 0 ? rowptr_f : rowptr_b;
+        uint2* rec    = dir == 0 ? fwd_rec : bwd_rec;
+#pragma unroll
+        for (int k = 0; k < kFastItems; k++) {
+            const int i = tid * kFastItems + k;
+            keys[k] = i < Eb ? ((unsigned)key_state[i] << kFastPosBits) | (unsigned)i : 0xffffffffu;
+        }
+        __syncthreads();  // the previous use of the sort storage is over
+        FastSort(sm.t.sort).Sort(keys);
+#pragma unroll
+        for (int k = 0; k < kFastItems; k++) {
+            const int j = tid * kFastItems + k;
+            sm.sorted[j] = keys[k];
+            if (j < Eb) {
+                const int i = (int)(keys[k] & pos_mask);
+                rec[e0 + j] = make_uint2((unsigned)other[i] | ((unsigned)sm.slot[i] << 16),
+                                         __float_as_uint(weights[qe[e0 + i]]));
+            }
+        }
+        __syncthreads();
+        // row pointers: first position whose state is >= s; the entry after the last state is the
+        // first entry of the next sequence (both write the same value)
+        int dmax = 0;
+        for (int s = tid; s <= Sb; s += kFastThreads) {
+            const unsigned want = (unsigned)s << kFastPosBits;
+            int lo = 0, hi = Eb;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (sm.sorted[mid] < want) lo = mid + 1; else hi = mid;
+            }
+            rowptr[s0 + s] = e0 + lo;
+            if (s < Sb) {
+                const unsigned nxt = (unsigned)(s + 1) << kFastPosBits;
+                int l2 = lo, h2 = Eb;
+                while (l2 < h2) {
+                    const int mid = (l2 + h2) >> 1;
+                    if (sm.sorted[mid] < nxt) l2 = mid + 1; else h2 = mid;
+                }
+                dmax = max(dmax, l2 - lo);
+            }
+        }
+        if (dmax > 0) atomicMax(&sm.deg_max, dmax);
+        __syncthreads();
+    }
+    for (int i = tid; i < Eb; i += kFastThreads) {
+        q_rec[e0 + i] = make_int4((int)sm.from[i], (int)sm.to[i], (int)sm.slot[i],
+                                  __float_as_int(weights[qe[e0 + i]]));
+    }
+    if (tid == 0 && sm.deg_max > 0) {
+        atomicMax((unsigned long long*)&hdr->max_degree, (unsigned long long)sm.deg_max);
     }
 }
 
@@ -567,7 +744,7 @@ struct RunArgs {
     float*       loss2;
     float *A, *Bt, *Gt, *Gf, *P, *X, *N;
     int* status;  // device status word of the call (0 = ok)
-    const int *state_off, *edge_off, *slot_off, *seq_T, *start_l, *end_l;
+    const int *state_off, *edge_off, *slot_off, *nslot, *seq_T, *start_l, *end_l;
     const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off, *tx_off;
     const int2* m_pos;
     const int *rowptr_f, *rowptr_b;
@@ -592,7 +769,7 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
         const int b   = a.order[rk];
         const int r   = (int)(u - a.gu_off[rk]);
         const int so  = a.slot_off[b];
-        const int Db  = a.slot_off[b + 1] - so;
+        const int Db  = a.nslot[b];
         const int Dp  = (Db + 3) & ~3;
         const int nch = (Db + kGatherSlots - 1) / kGatherSlots;
         const int k = r / nch, c = r % nch;
@@ -660,7 +837,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     if (Te == 0) return;
     const int s0 = a.state_off[b], Sb = a.state_off[b + 1] - s0;
     const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
-    const int Db = a.slot_off[b + 1] - a.slot_off[b];
+    const int Db = a.nslot[b];
     const int Dp = (Db + 3) & ~3;
     const int NT = blockDim.x, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
@@ -869,7 +1046,7 @@ __device__ __forceinline__ PostUnit post_unit(const RunArgs& a, i64 u) {
     p.e0 = a.edge_off[p.b];
     p.Eb = a.edge_off[p.b + 1] - p.e0;
     p.so = a.slot_off[p.b];
-    p.Db = a.slot_off[p.b + 1] - p.so;
+    p.Db = a.nslot[p.b];
     p.Dp = (p.Db + 3) & ~3;
     p.Te = a.seq_T[p.b];
     return p;
@@ -1040,8 +1217,8 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
         const i64  r  = (i64)t * B + b;
         const bool valid = t < a.seq_T[b];
         const int  so = a.slot_off[b];
-        const int  Db = valid ? a.slot_off[b + 1] - so : 0;
-        const int  Dp = ((a.slot_off[b + 1] - so) + 3) & ~3;
+        const int  Db = valid ? a.nslot[b] : 0;
+        const int  Dp = (a.nslot[b] + 3) & ~3;
         const int* __restrict__ emis = a.slot_emis + so;
         const float* __restrict__ Pr = a.P + a.gf_off[b] + (i64)t * Dp;
         const i64 rbase = r * F;
@@ -1338,6 +1515,7 @@ const char* fbw_b200_status_string(int status) {
         case FBW_B200_CUDA_ERROR: return "CUDA runtime error";
         case FBW_B200_BAD_AUTOMATON: return "automaton rejected (index out of range, state shared by two sequences, or a sequence too large)";
         case FBW_B200_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+        case FBW_B200_RETRY_GENERAL: return "plan must be rebuilt with fbw_b200_prepare_general";
         default: return "unknown status";
     }
 }
@@ -1347,9 +1525,10 @@ size_t fbw_b200_plan_bytes(int64_t B, int64_t E, int64_t S) {
     return plan_layout(B, E, S).total;
 }
 
-int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* start_end,
-                     const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E, int64_t S,
-                     void* plan, size_t plan_bytes, fbw_b200_stream_t stream) {
+static int prepare_impl(const int32_t* edges, const float* weights, const int32_t* start_end,
+                        const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E,
+                        int64_t S, void* plan, size_t plan_bytes, fbw_b200_stream_t stream,
+                        bool allow_fast) {
     if (T <= 0 || B <= 0 || F <= 0 || S <= 0 || E < 0) return FBW_B200_BAD_ARGUMENT;
     if (B > 0x7fffffff / 2 || E > 0x7fffffff - 1 || S > 0x7fffffff - 1 || T > 0x7fffffff)
         return FBW_B200_BAD_ARGUMENT;
@@ -1360,22 +1539,29 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
     if (plan_bytes < L.total) return FBW_B200_WORKSPACE;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
+    // Fast path: the edges are grouped by sequence with one device-wide sort and every sequence is
+    // then sorted three ways by one CTA in shared memory (k_seqsort).  It needs every sequence to
+    // have at most kFastCap edges; the host can only judge the average, a sequence over the limit
+    // flags the plan for a retry through the general path.
+    const bool fast = allow_fast && E > 0 && E / B <= kFastCap / 2 && F <= (i64)(1u << (32 - kFastPosBits));
+
     fbw_b200_summary* hdr = at<fbw_b200_summary>(plan, L.header);
     CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(fbw_b200_summary), st));
     CUDA_OK(cudaMemsetAsync(at<int>(plan, L.state_key), 0xff, 4 * (size_t)S, st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.scount), 0, 4 * (size_t)(B + 1), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.ecount), 0, 4 * (size_t)(B + 1), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_f), 0, 4 * (size_t)(S + 1), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_b), 0, 4 * (size_t)(S + 1), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.hs), 0, 4 * (size_t)(E + 1), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.m_ptr), 0, 4 * (size_t)(E + 1), st));
+    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.scount), 0, L.state_off - L.scount, st));  // scount, ecount
+    if (!fast) {
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_f), 0, 4 * (size_t)(S + 1), st));
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_b), 0, 4 * (size_t)(S + 1), st));
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.hs), 0, 4 * (size_t)(E + 1), st));
+        CUDA_OK(cudaMemsetAsync(at<int>(plan, L.m_ptr), 0, 4 * (size_t)(E + B + 1), st));
+    }
 
     const int TB = 256;
     auto blocks = [&](i64 n) { return (unsigned)((n + TB - 1) / TB); };
     void*  ctemp = at<char>(plan, L.cub_temp);
     size_t cbytes = L.cub_temp_bytes;
 
-    COUNT_LAUNCH(E > 0 ? 9 : 5);  // k_mark, k_off1, k_statekeys, k_packed, k_off2 (+4 edge kernels)
+    COUNT_LAUNCH(fast ? 7 : (E > 0 ? 9 : 5));  // k_mark, k_off1, k_statekeys, k_packed, k_off2 + edge kernels
     k_mark<<<blocks(E + B), TB, 0, st>>>(edges, start_end, E, B, S, F, at<int>(plan, L.state_key),
                                          at<int>(plan, L.scount), at<int>(plan, L.ecount), hdr);
     k_off1<<<1, 1024, 0, st>>>(at<int>(plan, L.scount), at<int>(plan, L.ecount), seq_lens, (int)B,
@@ -1389,7 +1575,29 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
                                             at<int>(plan, L.siota), at<int>(plan, L.sorted_state),
                                             (int)S, 0, bits_for((unsigned long long)B), st));
     k_packed<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.sorted_state), S, at<int>(plan, L.packed_of));
-    if (E > 0) {
+    if (fast) {
+        k_seqkeys<<<blocks(E), TB, 0, st>>>(edges, E, at<unsigned>(plan, L.keyq),
+                                            at<int>(plan, L.eiota), hdr);
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyq),
+                                                at<unsigned>(plan, L.key32_out),
+                                                at<int>(plan, L.eiota), at<int>(plan, L.qe), (int)E,
+                                                0, bits_for((unsigned long long)B), st));
+        static bool attr_set[64] = {false};
+        int dev = 0;
+        CUDA_OK(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            CUDA_OK(cudaFuncSetAttribute(k_seqsort, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)sizeof(FastSmem)));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
+        k_seqsort<<<(unsigned)B, kFastThreads, sizeof(FastSmem), st>>>(
+            edges, weights, E, F, at<int>(plan, L.qe), at<int>(plan, L.edge_off),
+            at<int>(plan, L.state_off), at<int>(plan, L.packed_of), at<int>(plan, L.rowptr_f),
+            at<int>(plan, L.rowptr_b), at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec),
+            at<int4>(plan, L.q_rec), at<int4>(plan, L.m_rec), at<int2>(plan, L.m_pos),
+            at<int>(plan, L.m_ptr), at<int>(plan, L.slot_emis), at<int>(plan, L.slot_off),
+            at<int>(plan, L.nslot), hdr);
+    } else if (E > 0) {
         k_edgekeys<<<blocks(E), TB, 0, st>>>(edges, E, F, at<int>(plan, L.packed_of),
                                              at<unsigned>(plan, L.keyq), at<unsigned>(plan, L.keyf),
                                              at<unsigned>(plan, L.keyb),
@@ -1434,13 +1642,14 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
     k_off2<<<1, 1024, 0, st>>>(at<int>(plan, L.state_off), at<int>(plan, L.edge_off),
                                at<int>(plan, L.hs), at<int>(plan, L.seq_T), start_end,
                                at<int>(plan, L.packed_of), (int)B, T, F, E, S,
-                               at<int>(plan, L.slot_off), at<int>(plan, L.start_l),
+                               at<int>(plan, L.slot_off), at<int>(plan, L.nslot),
+                               at<int>(plan, L.start_l),
                                at<int>(plan, L.end_l), at<i64>(plan, L.ta_off),
                                at<i64>(plan, L.tg_off), at<i64>(plan, L.gf_off),
                                at<i64>(plan, L.gu_off), at<i64>(plan, L.pu_off),
                                at<i64>(plan, L.tx_off), at<i64>(plan, L.cost),
-                               at<int>(plan, L.order), hdr);
-    if (E > 0) {
+                               at<int>(plan, L.order), fast ? 1 : 0, hdr);
+    if (E > 0 && !fast) {
         k_records<<<blocks(E), TB, 0, st>>>(
             edges, weights, E, at<int>(plan, L.packed_of), at<int>(plan, L.state_off),
             at<int>(plan, L.slot_off), at<int>(plan, L.slot_of_edge), at<int>(plan, L.qe),
@@ -1452,11 +1661,26 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
     return FBW_B200_OK;
 }
 
+int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* start_end,
+                     const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E, int64_t S,
+                     void* plan, size_t plan_bytes, fbw_b200_stream_t stream) {
+    return prepare_impl(edges, weights, start_end, seq_lens, T, B, F, E, S, plan, plan_bytes, stream,
+                        true);
+}
+
+int fbw_b200_prepare_general(const int32_t* edges, const float* weights, const int32_t* start_end,
+                             const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E,
+                             int64_t S, void* plan, size_t plan_bytes, fbw_b200_stream_t stream) {
+    return prepare_impl(edges, weights, start_end, seq_lens, T, B, F, E, S, plan, plan_bytes, stream,
+                        false);
+}
+
 int fbw_b200_plan_summary(const void* plan, fbw_b200_summary* summary, fbw_b200_stream_t stream) {
     if (!plan || !summary) return FBW_B200_BAD_ARGUMENT;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     CUDA_OK(cudaMemcpyAsync(summary, plan, sizeof(fbw_b200_summary), cudaMemcpyDeviceToHost, st));
     CUDA_OK(cudaStreamSynchronize(st));
+    if (summary->error == FBW_B200_ERR_RETRY_GENERAL) return FBW_B200_RETRY_GENERAL;
     return summary->error ? FBW_B200_BAD_AUTOMATON : FBW_B200_OK;
 }
 
@@ -1490,6 +1714,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.state_off = at<int>(plan, L.state_off);
     a.edge_off  = at<int>(plan, L.edge_off);
     a.slot_off  = at<int>(plan, L.slot_off);
+    a.nslot     = at<int>(plan, L.nslot);
     a.seq_T     = at<int>(plan, L.seq_T);
     a.start_l   = at<int>(plan, L.start_l);
     a.end_l     = at<int>(plan, L.end_l);

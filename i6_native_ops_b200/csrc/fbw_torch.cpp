@@ -89,6 +89,15 @@ Prepared prepare_impl(const torch::Tensor& edges, const torch::Tensor& weights,
                                   reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
     int st = fbw_b200_plan_summary(p.plan.data_ptr(), &p.summary,
                                    reinterpret_cast<fbw_b200_stream_t>(stream.stream()));
+    if (st == FBW_B200_RETRY_GENERAL) {  // a sequence too large for the fast plan builder
+        check_status(fbw_b200_prepare_general(
+            edges.data_ptr<int32_t>(), weights.data_ptr<float>(),
+            start_end_states.data_ptr<int32_t>(), seq_lens.data_ptr<int32_t>(), T, B, F, E,
+            num_states, p.plan.data_ptr(), pbytes,
+            reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+        st = fbw_b200_plan_summary(p.plan.data_ptr(), &p.summary,
+                                   reinterpret_cast<fbw_b200_stream_t>(stream.stream()));
+    }
     check_status(st, &p.summary);
     return p;
 }

@@ -39,7 +39,9 @@ enum {
     FBW_B200_CUDA_ERROR     = 3, /* a CUDA runtime call failed (see cudaGetLastError)            */
     FBW_B200_BAD_AUTOMATON  = 4, /* summary.error != 0: an index in edges/start_end out of range,
                                     a state used by two sequences, or a per-sequence size limit */
-    FBW_B200_TOO_LARGE      = 5  /* request exceeds the fixed capacity of a no-allocation entry  */
+    FBW_B200_TOO_LARGE      = 5, /* request exceeds the fixed capacity of a no-allocation entry  */
+    FBW_B200_RETRY_GENERAL  = 6  /* fbw_b200_prepare took its fast path and a sequence did not fit it:
+                                    call fbw_b200_prepare_general with the same arguments        */
 };
 
 /* Bits of fbw_b200_summary.error (validation of the automata; the reference does not validate,
@@ -50,7 +52,8 @@ enum {
     FBW_B200_ERR_SEQ_RANGE      = 4,  /* sequence id outside [0, B)                       */
     FBW_B200_ERR_START_END      = 8,  /* start or end state outside [0, S)                */
     FBW_B200_ERR_SHARED_STATE   = 16, /* one state id used by edges of two sequences      */
-    FBW_B200_ERR_SEQ_TOO_LARGE  = 32  /* a sequence has more than 65535 states or classes */
+    FBW_B200_ERR_SEQ_TOO_LARGE  = 32, /* a sequence has more than 65535 states or classes */
+    FBW_B200_ERR_RETRY_GENERAL  = 64  /* not an input error: see FBW_B200_RETRY_GENERAL    */
 };
 
 #define FBW_B200_GROUPS 8
@@ -86,8 +89,17 @@ int fbw_b200_prepare(const int32_t* edges, const float* weights, const int32_t* 
                      const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E, int64_t S,
                      void* plan, size_t plan_bytes, fbw_b200_stream_t stream);
 
+/* The same, always through the general path (device-wide radix sorts; any sequence size within the
+ * limits above).  fbw_b200_prepare itself picks a faster path (one CTA sorts one sequence in shared
+ * memory) when the average sequence is small; if a single sequence then exceeds that path's capacity
+ * (4096 edges), fbw_b200_plan_summary returns FBW_B200_RETRY_GENERAL and this call redoes the plan. */
+int fbw_b200_prepare_general(const int32_t* edges, const float* weights, const int32_t* start_end,
+                             const int32_t* seq_lens, int64_t T, int64_t B, int64_t F, int64_t E,
+                             int64_t S, void* plan, size_t plan_bytes, fbw_b200_stream_t stream);
+
 /* Copy the plan's summary to host memory.  SYNCHRONISES the stream.  Returns
- * FBW_B200_BAD_AUTOMATON if validation failed (summary->error says why). */
+ * FBW_B200_BAD_AUTOMATON if validation failed (summary->error says why), FBW_B200_RETRY_GENERAL if
+ * the plan has to be redone with fbw_b200_prepare_general. */
 int fbw_b200_plan_summary(const void* plan, fbw_b200_summary* summary, fbw_b200_stream_t stream);
 
 /* Bytes of run scratch for a prepared plan. */
