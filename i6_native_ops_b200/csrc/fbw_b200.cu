@@ -75,6 +75,12 @@ struct PlanLayout {
 };
 
 size_t cub_temp_need(i64 E, i64 S) {
+    // the answer depends on (E, S) only; one call asks three times per op call, so remember the last
+    static std::mutex mu;
+    static i64 last_E = -1, last_S = -1;
+    static size_t last_need = 0;
+    std::lock_guard<std::mutex> lk(mu);
+    if (E == last_E && S == last_S) return last_need;
     size_t need = 0, b = 0;
     int    nE = (int)(E > 0 ? E : 1), nS = (int)(S > 0 ? S : 1);
     cub::DeviceRadixSort::SortPairs(nullptr, b, (const unsigned*)nullptr, (unsigned*)nullptr,
@@ -87,6 +93,7 @@ size_t cub_temp_need(i64 E, i64 S) {
     cub::DeviceScan::ExclusiveSum(nullptr, b, (const int*)nullptr, (int*)nullptr,
                                   (nE > nS ? nE : nS) + 1);
     need = b > need ? b : need;
+    last_E = E; last_S = S; last_need = need;
     return need;
 }
 
@@ -411,9 +418,11 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
     __shared__ typename Scan::TempStorage tmp;
     __shared__ i64 carry[8];
     __shared__ int smax[4];
+    __shared__ int smin;
     __shared__ int gmax[3][FBW_B200_GROUPS];
     if (threadIdx.x < 8) carry[threadIdx.x] = 0;
     if (threadIdx.x < 4) smax[threadIdx.x] = 0;
+    if (threadIdx.x == 0) smin = 0x7fffffff;
     if (threadIdx.x < 3 * FBW_B200_GROUPS) (&gmax[0][0])[threadIdx.x] = 0;
     __syncthreads();
     const bool bad = hdr->error != 0;
@@ -449,6 +458,7 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
             atomicMax(&smax[1], Eb);
             atomicMax(&smax[2], Db);
             atomicMax(&smax[3], Te);
+            if (Te > 0) atomicMin(&smin, Te);
         }
         i64* dst[6] = {ta_off, tg_off, gf_off, nullptr, tx_off, nullptr};
         for (int k = 0; k < 6; k++) {
@@ -522,6 +532,7 @@ __global__ void __launch_bounds__(1024) k_off2(const int* __restrict__ state_off
         hdr->max_edges  = smax[1];
         hdr->max_slots  = smax[2];
         hdr->max_len    = smax[3];
+        hdr->min_len    = smin == 0x7fffffff ? 0 : smin;
         for (int g = 0; g < FBW_B200_GROUPS; g++) {
             hdr->group_max_states[g] = gmax[0][g];
             hdr->group_max_edges[g]  = gmax[1][g];
@@ -753,7 +764,28 @@ struct RunArgs {
     const int *m_ptr, *slot_emis, *order;
     i64 T, B, F;
     int r0, r1;  // rank range (a group of sequences) this launch works on
+    // Time chunks: the sweeps advance chunk_steps frames per chunk from both ends of a sequence; a
+    // launch handles the chunks [c_lo, c_hi).  One chunk covering everything is the plain case.
+    int c_lo, c_hi, chunk_steps;
+    float* carry;  // state vectors handed from one sweep chunk to the next, [2 * state][direction]
 };
+
+// chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
+// sweep reaches frame 32k at step 32k, the backward sweep reaches the tile's last frame at step
+// Te - 1 - last
+__device__ __forceinline__ int tile_need_chunk(int k, int Te, int J) {
+    const int last = min(k * kTile + kTile - 1, Te - 1);
+    return min((k * kTile) / J, (Te - 1 - last) / J);
+}
+// chunk after which both alpha and beta of every frame of tile k are known: the forward sweep
+// finishes the tile in the chunk of its last frame, the backward sweep in the chunk of step
+// Te - 1 - 32k
+__device__ __forceinline__ int tile_done_chunk(int k, int Te, int J) {
+    const int last = min(k * kTile + kTile - 1, Te - 1);
+    return max(last / J, (Te - 1 - k * kTile) / J);
+}
+__device__ __forceinline__ bool in_chunks(int c, const RunArgs& a) { return c >= a.c_lo && c < a.c_hi; }
+
 
 // Gather am_scores[t,b,emission] for the distinct emissions ("slots", ascending emission id) of
 // each sequence.  Work item = (sequence, 32-frame tile, 256 slots).  Two copies are written:
@@ -774,6 +806,7 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
         const int nch = (Db + kGatherSlots - 1) / kGatherSlots;
         const int k = r / nch, c = r % nch;
         const int Te = a.seq_T[b];
+        if (!in_chunks(tile_need_chunk(k, Te, a.chunk_steps), a)) continue;  // uniform in the CTA
         const int d0 = c * kGatherSlots;
         const int nd = min(kGatherSlots, Db - d0);
         const int* __restrict__ emis = a.slot_emis + so + d0;
@@ -863,12 +896,22 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     auto srow = [&](int j, int t) -> float* {
         return sbase + (size_t)(TILED ? (t & 63) : (j & 1)) * spad;
     };
+    // this launch covers steps [j0, j1) of the sequence's Te steps (a time chunk); a later chunk
+    // picks up the state vector the previous one left in `carry`
+    const int j0 = a.c_lo * a.chunk_steps;
+    const int j1 = (int)min((i64)a.c_hi * a.chunk_steps, (i64)Te);
+    if (j0 >= Te) return;
+    float* __restrict__ carry = a.carry + 2 * (i64)s0 + (fwd ? 0 : Sb);
     {
         const int seed = fwd ? a.start_l[b] : a.end_l[b];
-        float* r0 = srow(0, t_first);
-        for (int s = tid; s < Sb; s += NT) r0[s] = (s == seed) ? 0.f : CUDART_INF_F;
+        float* r0 = srow(j0, t_first + step * j0);
+        for (int s = tid; s < Sb; s += NT) {
+            r0[s] = j0 == 0 ? ((s == seed) ? 0.f : CUDART_INF_F) : carry[s];
+        }
     }
     __syncthreads();
+    // frames this launch records, for the tiled flush
+    const int f_lo = fwd ? j0 : Te - j1, f_hi = fwd ? j1 - 1 : Te - 1 - j0;
 
     // the first state of this thread: its edges live in registers
     int   rfrom[kRegEdges], rslot[kRegEdges];
@@ -908,7 +951,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     };
     if (RING > 0) {
 #pragma unroll
-        for (int j = 0; j < RING - 1; j++) issue(j);
+        for (int j = 0; j < RING - 1; j++) issue(j0 + j);
     }
     // write frames lo..hi (all inside tile k) of the shared-memory ring out as [state][32] lines
     auto flush_tile = [&](int k, int lo, int hi) {
@@ -922,7 +965,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     };
 
     constexpr int kWait = RING > 1 ? RING - 2 : 0;
-    for (int j = 0; j < Te; j++) {
+    for (int j = j0; j < j1; j++) {
         const int t = t_first + step * j;
         if (RING > 0) cp_async_wait<kWait>();
         __syncthreads();
@@ -932,7 +975,8 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             float* drow = dst + ((i64)(t >> 5) * Sb) * kTile + (t & 31);
             for (int s = tid; s < Sb; s += NT) drow[(i64)s * kTile] = cur[s];
         }
-        const bool last = j == Te - 1;
+        const bool last  = j == Te - 1;           // the sequence ends here: nothing to compute
+        const bool hand  = j == j1 - 1 && !last;  // a later chunk continues from the next vector
         if (!last) {
             float* nxt = srow(j + 1, t + step);
             const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
@@ -956,6 +1000,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
                     }
                 }
                 nxt[tid] = acc;
+                if (hand) carry[tid] = acc;
             }
             for (int s = tid + NT; s < Sb; s += NT) {
                 float acc = CUDART_INF_F;
@@ -968,17 +1013,14 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
                     }
                 }
                 nxt[s] = acc;
+                if (hand) carry[s] = acc;
             }
         }
-        if (TILED) {
+        if (TILED) {  // a tile is written when the sweep leaves it or the launch ends
             const int k = t >> 5;
-            if (fwd) {
-                if ((t & 31) == 31 || last) flush_tile(k, k * kTile, t);
-            } else {
-                if ((t & 31) == 0) flush_tile(k, t, min(k * kTile + 31, Te - 1));
-            }
+            const bool out_now = fwd ? ((t & 31) == 31 || j == j1 - 1) : ((t & 31) == 0 || j == j1 - 1);
+            if (out_now) flush_tile(k, max(k * kTile, f_lo), min(k * kTile + 31, f_hi));
         }
-        if (last) break;
     }
     if (RING > 0) cp_async_wait<0>();
 }
@@ -1063,6 +1105,7 @@ __global__ void __launch_bounds__(256) k_score(RunArgs a) {
     const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
     for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
         const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
         const bool valid = p.k * kTile + lane < p.Te;
         // every lane loads (a tile is allocated for all 32 frames); frames past the sequence's
         // length hold unspecified values and get +inf
@@ -1103,6 +1146,7 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
     const i64 W = (i64)gridDim.x * 4;
     for (i64 idx = (i64)blockIdx.x * 4 + warp; idx < nunits; idx += W) {
         const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
         const int  t     = p.k * kTile + lane;
         const bool valid = t < p.Te;
         const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
@@ -1140,6 +1184,7 @@ __global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
     const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
     for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
         const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
         const float acc = a.N[p.u * kTile + lane];
         const bool rowdead = !(acc < CUDART_INF_F);  // no path through this frame
         const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
@@ -1209,11 +1254,24 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
     float* seg = segs[warp];
     for (int i = lane; i < kSegFloats; i += 32) seg[i] = CUDART_INF_F;
     __syncwarp();
+    // Work item of a CTA: (32-frame tile, sequence), all T frames (frames past a sequence's length
+    // are +inf rows).  A tile is written once the posteriors of its frames exist, i.e. in the chunk
+    // after which both sweeps have passed it; tiles past the sequence's length go with chunk 0.
     const int nb  = a.r1 - a.r0;  // sequences of this group
-    const i64 rows = a.T * nb;
-    for (i64 i = (i64)blockIdx.x * 8 + warp; i < rows; i += (i64)gridDim.x * 8) {
-        const int  t  = (int)(i / nb);
-        const int  b  = a.order[a.r0 + (int)(i - (i64)t * nb)];
+    const int ntT = (int)((a.T + kTile - 1) / kTile);
+    const i64 items = (i64)ntT * nb * 4;  // a work item per quarter tile (8 rows, one per warp)
+    for (i64 it = blockIdx.x; it < items; it += gridDim.x) {
+        const int  qt = (int)(it & 3);
+        const i64  un = it >> 2;
+        const int  k  = (int)(un / nb);
+        const int  b  = a.order[a.r0 + (int)(un - (i64)k * nb)];
+        {
+            const int Te  = a.seq_T[b];
+            const int dch = k * kTile < Te ? tile_done_chunk(k, Te, a.chunk_steps) : 0;
+            if (!in_chunks(dch, a)) continue;  // uniform in the CTA
+        }
+        const int  t  = k * kTile + qt * 8 + warp;
+        if (t >= a.T) continue;
         const i64  r  = (i64)t * B + b;
         const bool valid = t < a.seq_T[b];
         const int  so = a.slot_off[b];
@@ -1259,7 +1317,7 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
 #pragma unroll
             for (int i = 0; i < kSegFloats / 128; i++) {
                 const int vi = lane + 32 * i;
-                if (vi < nv) dst4[vi] = src4[vi];
+                if (vi < nv) __stcs(dst4 + vi, src4[vi]);
             }
             __syncwarp();
             for (int d = dstart + lane; d < dlo; d += 32) seg[emis[d] - cs] = CUDART_INF_F;
@@ -1304,7 +1362,7 @@ __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i
 // host side
 // ---------------------------------------------------------------------------------------------
 struct RunLayout {
-    size_t status, A, Bt, Gt, Gf, P, X, N, total;
+    size_t status, A, Bt, Gt, Gf, P, X, N, carry, total;
 };
 
 RunLayout run_layout(const fbw_b200_summary& s) {
@@ -1323,6 +1381,7 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     L.P     = take((size_t)s.frame_floats);
     L.X     = take((size_t)s.score_floats);
     L.N     = take((size_t)s.post_units * kTile);
+    L.carry = take((size_t)(2 * s.S));
     L.total = off;
     return L;
 }
@@ -1369,12 +1428,16 @@ int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int 
     return launch_sweep_k<RING, TILED, 4>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
 }
 
+constexpr int kMaxChunks = 16;
+constexpr int kPostStreams = 4;  // aux[1..4] carry the output stages, aux[0] the gather
+
 // streams and events for the per-group pipelines, one pool per device, created on first use
 struct StreamPool {
     std::mutex   mu;
     bool         ready = false, failed = false;
     cudaStream_t aux[FBW_B200_GROUPS];
     cudaEvent_t  fork, join[FBW_B200_GROUPS];
+    cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks];
 };
 StreamPool g_pools[64];
 std::mutex g_pools_mu;
@@ -1391,6 +1454,10 @@ StreamPool* stream_pool() {
             ok = cudaStreamCreateWithFlags(&p->aux[i], cudaStreamNonBlocking) == cudaSuccess &&
                  cudaEventCreateWithFlags(&p->join[i], cudaEventDisableTiming) == cudaSuccess;
         }
+        for (int i = 0; i < kMaxChunks && ok; i++) {
+            ok = cudaEventCreateWithFlags(&p->gathered[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&p->swept[i], cudaEventDisableTiming) == cudaSuccess;
+        }
         if (!ok) {
             p->failed = true;
             return nullptr;
@@ -1400,37 +1467,43 @@ StreamPool* stream_pool() {
     return p;
 }
 
-// number of launch groups (1, 2, 4 or 8): small calls stay on one stream
-int choose_groups(const fbw_b200_summary& s) {
+// number of time chunks of the pipeline: small calls run as one chunk on the caller's stream
+int choose_chunks(const fbw_b200_summary& s) {
     static int forced = -1;
     if (forced < 0) {
-        const char* e = getenv("FBW_B200_NUM_GROUPS");
+        const char* e = getenv("FBW_B200_NUM_CHUNKS");
         forced = e ? atoi(e) : 0;
     }
-    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return forced;
+    int C = 1;
     const double cells = (double)s.T * (double)s.B * (double)s.F;
-    if (s.B >= 16 && cells >= 1.0e8) return 4;
-    return 1;
+    if (cells >= 1.0e8 && s.max_len >= 512) C = 8;
+    if (forced >= 1) C = forced;
+    if (C > kMaxChunks) C = kMaxChunks;
+    while (C > 1 && s.max_len / C < 2 * kTile) C--;  // at least two tiles per chunk
+    return C;
 }
 
 // gather -> sweep -> posterior -> expand for the sequences of ranks [r0, r1) on stream st.
 // ms/me/md: largest state, edge and slot counts in the range (they size the sweep launch).
+enum { kDoGather = 1, kDoSweep = 2, kDoPost = 4, kDoExpand = 8, kDoAll = 15 };
+
+// `what` selects the stages to launch (the time-chunked pipeline launches them on different streams)
 int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b200_summary& s,
-                 cudaStream_t st, cudaEvent_t* ev) {
+                 cudaStream_t st, cudaEvent_t* ev, int what = kDoAll) {
     const int sms = sm_count();
     const int nb  = r1 - r0;
     a.r0 = r0;
     a.r1 = r1;
     const i64 tiles = (s.max_len + kTile - 1) / kTile;
     if (ev) CUDA_OK(cudaEventRecord(ev[0], st));
-    if (s.gather_units > 0 && md > 0) {
+    if ((what & kDoGather) && s.gather_units > 0 && md > 0) {
         i64 want = tiles * nb * ((md + kGatherSlots - 1) / kGatherSlots);
         int grid = (int)(want < (i64)sms * 6 ? want : (i64)sms * 6);
         k_gather<<<grid > 0 ? grid : 1, 256, 0, st>>>(a);
         COUNT_LAUNCH(1);
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
-    if (s.max_len > 0) {
+    if ((what & kDoSweep) && s.max_len > 0) {
         int smax  = (int)((ms + 3) & ~3);
         int dpmax = (int)((md + 3) & ~3);
         int nt    = (int)((ms + 31) & ~31);
@@ -1480,7 +1553,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         if (rc != FBW_B200_OK) return rc;
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[2], st));
-    if (s.post_units > 0) {
+    if ((what & kDoPost) && s.post_units > 0) {
         const i64 units = tiles * nb;  // upper bound; the kernels read the exact count
         int g1 = (int)(units < (i64)sms * 8 ? units : (i64)sms * 8);
         k_score<<<g1 > 0 ? g1 : 1, 256, 0, st>>>(a);
@@ -1492,8 +1565,8 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         COUNT_LAUNCH(3);
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
-    {
-        i64 want = (s.T * nb + 7) / 8;
+    if (what & kDoExpand) {
+        i64 want = ((s.T + kTile - 1) / kTile) * nb * 4;
         int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
         k_expand<<<grid, 256, 0, st>>>(a);
         COUNT_LAUNCH(1);
@@ -1710,6 +1783,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.P  = at<float>(work, R.P);
     a.X  = at<float>(work, R.X);
     a.N  = at<float>(work, R.N);
+    a.carry = at<float>(work, R.carry);
     a.status = at<int>(work, R.status);
     a.state_off = at<int>(plan, L.state_off);
     a.edge_off  = at<int>(plan, L.edge_off);
@@ -1736,49 +1810,69 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.order     = at<int>(plan, L.order);
     a.T = s.T; a.B = s.B; a.F = s.F;
     a.r0 = 0; a.r1 = (int)s.B;
+    a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
 
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
     CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
 
-    // Sequence groups (rank ranges of similar cost) run as independent pipelines
-    // gather -> sweep -> scores -> posteriors -> expand on their own streams, so that one group's
-    // arithmetic-bound posterior pass overlaps another's memory-bound output pass.  With phase
-    // events everything runs as one group on the caller's stream.
-    int G = ev ? 1 : choose_groups(s);
-    StreamPool* pool = nullptr;
-    std::unique_lock<std::mutex> lock;
-    if (G > 1) {
-        pool = stream_pool();
-        if (!pool) {
-            G = 1;
-        } else {
-            lock = std::unique_lock<std::mutex>(pool->mu);
-            CUDA_OK(cudaEventRecord(pool->fork, st));
-        }
+    // Large calls run as a pipeline over time chunks: both sweeps advance `chunk_steps` frames per
+    // chunk from the two ends of every sequence.  The gather of the scores a chunk needs runs one
+    // chunk ahead on a second stream, and once the sweeps have crossed, the tiles whose alpha and
+    // beta are both known are scored, normalised and written out on a third stream while the sweeps
+    // go on.  The sweeps are arithmetic-bound, the gather and the output pass memory-bound, so they
+    // overlap well; only the first gather chunk and the last output chunk are exposed.
+    const int C = ev ? 1 : choose_chunks(s);
+    i64 ms = 0, me = 0, md = 0;
+    for (int q = 0; q < FBW_B200_GROUPS; q++) {
+        ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
+        me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
+        md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
     }
-    const int per = FBW_B200_GROUPS / G;  // base groups merged into one launch group
-    for (int g = 0; g < G; g++) {
-        const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
-        const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
-        if (r1 <= r0) continue;
-        i64 ms = 0, me = 0, md = 0;
-        for (int q = g * per; q < (g + 1) * per; q++) {
-            ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
-            me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
-            md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
+    StreamPool* pool = C > 1 ? stream_pool() : nullptr;
+    if (C > 1 && pool) {
+        std::unique_lock<std::mutex> lock(pool->mu);
+        a.chunk_steps = (int)(((s.max_len + C - 1) / C + kTile - 1) / kTile * kTile);
+        const i64 J = a.chunk_steps;
+        // chunks that can have work: scores are first needed before the sweeps cross (the middle
+        // of the longest sequence); tiles are complete only after the sweeps of the shortest
+        // sequence have crossed
+        const int last_gather  = (int)((s.max_len / 2 + kTile) / J);
+        const int first_finish = (int)((s.min_len / 2 - kTile > 0 ? s.min_len / 2 - kTile : 0) / J);
+        cudaStream_t gs = pool->aux[0];
+        CUDA_OK(cudaEventRecord(pool->fork, st));
+        CUDA_OK(cudaStreamWaitEvent(gs, pool->fork, 0));
+        for (int i = 1; i <= kPostStreams; i++) CUDA_OK(cudaStreamWaitEvent(pool->aux[i], pool->fork, 0));
+        for (int c = 0; c < C; c++) {
+            a.c_lo = c;
+            a.c_hi = c + 1;
+            int rc;
+            if (c <= last_gather) {
+                rc = launch_group(a, 0, (int)s.B, ms, me, md, s, gs, nullptr, kDoGather);
+                if (rc != FBW_B200_OK) return rc;
+                CUDA_OK(cudaEventRecord(pool->gathered[c], gs));
+                CUDA_OK(cudaStreamWaitEvent(st, pool->gathered[c], 0));
+            }
+            rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, nullptr, kDoSweep);
+            if (rc != FBW_B200_OK) return rc;
+            // the output stages of successive chunks go to different streams: each stage is a
+            // chain of latency-bound kernels, several chunks' chains have to be in flight at once
+            if (c == 0 || c >= first_finish) {
+                cudaStream_t ps = pool->aux[1 + c % kPostStreams];
+                CUDA_OK(cudaEventRecord(pool->swept[c], st));
+                CUDA_OK(cudaStreamWaitEvent(ps, pool->swept[c], 0));
+                rc = launch_group(a, 0, (int)s.B, ms, me, md, s, ps, nullptr,
+                                  c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
+                if (rc != FBW_B200_OK) return rc;
+            }
         }
-        cudaStream_t gs = st;
-        if (g > 0) {
-            gs = pool->aux[g];
-            CUDA_OK(cudaStreamWaitEvent(gs, pool->fork, 0));
+        for (int i = 1; i <= kPostStreams; i++) {
+            CUDA_OK(cudaEventRecord(pool->join[i], pool->aux[i]));
+            CUDA_OK(cudaStreamWaitEvent(st, pool->join[i], 0));
         }
-        int rc = launch_group(a, r0, r1, ms, me, md, s, gs, ev);
+    } else {
+        int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kDoAll);
         if (rc != FBW_B200_OK) return rc;
-        if (g > 0) {
-            CUDA_OK(cudaEventRecord(pool->join[g], gs));
-            CUDA_OK(cudaStreamWaitEvent(st, pool->join[g], 0));
-        }
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[4], st));
     if (loss2) {

@@ -103,11 +103,12 @@ Prepared prepare_impl(const torch::Tensor& edges, const torch::Tensor& weights,
 }
 
 std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_scores,
-                                    bool want_loss) {
+                                    bool want_loss, torch::Tensor out = torch::Tensor(),
+                                    torch::Tensor sums = torch::Tensor()) {
     auto stream = at::cuda::getCurrentCUDAStream();
     const fbw_b200_summary& s = p.summary;
-    torch::Tensor out  = torch::empty_like(am_scores);
-    torch::Tensor sums = torch::empty({s.T, s.B}, am_scores.options());
+    if (!out.defined()) out = torch::empty_like(am_scores);
+    if (!sums.defined()) sums = torch::empty({s.T, s.B}, am_scores.options());
     torch::Tensor loss2;
     if (want_loss) loss2 = torch::empty({2}, am_scores.options());
     size_t wbytes = fbw_b200_run_bytes(&s);
@@ -135,9 +136,12 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
                 "start_end_states must have shape (2, B) with B = am_scores.size(1)");
     c10::cuda::CUDAGuard guard(am_scores.device());
     (void)debug_options;  // text dumps (fbw_op.cu:155-224) are not produced
+    // the outputs do not depend on the plan: allocate them while the plan is still being built
+    torch::Tensor out  = torch::empty_like(am_scores);
+    torch::Tensor sums = torch::empty({am_scores.size(0), am_scores.size(1)}, am_scores.options());
     Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, am_scores.size(0),
                               am_scores.size(2), (int64_t)num_states);
-    return run_impl(p, am_scores, false);
+    return run_impl(p, am_scores, false, out, sums);
 }
 
 // Two-step form of the same op for callers that reuse one batch of automata with new scores:

@@ -74,7 +74,8 @@ typedef struct fbw_b200_summary {
     int64_t group_max_states[8], group_max_edges[8], group_max_slots[8];
     int64_t max_degree;   /* largest in-degree or out-degree of a state                           */
     int64_t score_floats; /* floats in the per-frame edge-score array                              */
-    int64_t reserved[2];
+    int64_t min_len;      /* shortest valid sequence length (0 if none)                           */
+    int64_t reserved[1];
 } fbw_b200_summary;
 
 /* Bytes of plan scratch for B sequences, E edges, S states. */
