@@ -46,7 +46,7 @@ namespace {
 
 constexpr int kTile        = 32;   // frames per tile of the tiled layouts (= one lane per frame)
 constexpr int kGatherSlots = 256;  // classes per gather work item
-constexpr int kSegFloats   = 512;  // floats per output segment composed in shared memory
+constexpr int kSegFloats   = 256;  // floats per output segment composed in shared memory
 constexpr int kMaxPerSeq   = 65535;
 
 typedef long long i64;
@@ -1247,13 +1247,11 @@ __global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
 // row is split into a scalar head, a 16-byte aligned body and a scalar tail.  One pass over the
 // output instead of the reference's zeros_like + fill + atomics (fbw_op.cu:230, 366-378).
 __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
-    __shared__ __align__(16) float segs[8][kSegFloats];
+    __shared__ __align__(128) float segs[8][2][kSegFloats];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int B = (int)a.B;
     const i64 F = a.F;
-    float* seg = segs[warp];
-    for (int i = lane; i < kSegFloats; i += 32) seg[i] = CUDART_INF_F;
-    __syncwarp();
+    int which = 0;  // segment buffer in use; the other one may still be read by a store in flight
     // Work item of a CTA: (32-frame tile, sequence), all T frames (frames past a sequence's length
     // are +inf rows).  A tile is written once the posteriors of its frames exist, i.e. in the chunk
     // after which both sweeps have passed it; tiles past the sequence's length go with chunk 0.
@@ -1297,10 +1295,22 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
             if (lane < head) row[lane] = v;
             while (dlo < Db && emis[dlo] < head) dlo++;
         }
-        // aligned body
+        // aligned body: compose 512 floats in shared memory, hand them to the copy engine
+        // (cp.async.bulk shared -> global), and compose the next segment in the other buffer
+        // while that store is in flight
         for (i64 cs = head; cs < body_end; cs += kSegFloats) {
             const i64 ce = min(cs + (i64)kSegFloats, body_end);
-            const int dstart = dlo;
+            float* seg = segs[warp][which];
+            // the store issued from this buffer two segments ago must have read it
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            {
+                const float4 inf4 = make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F);
+                float4* s4 = reinterpret_cast<float4*>(seg);
+#pragma unroll
+                for (int i = 0; i < kSegFloats / 128; i++) s4[lane + 32 * i] = inf4;
+            }
+            __syncwarp();
             int n;
             do {  // patch the slots of this segment
                 const int d  = dlo + lane;
@@ -1310,18 +1320,17 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
                 n = __popc(__ballot_sync(0xffffffffu, in));
                 dlo += n;
             } while (n == 32);
+            // make the generic-proxy writes visible to the async proxy, then one lane issues
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            const int nv = (int)((ce - cs) >> 2);
-            float4* __restrict__ dst4 = reinterpret_cast<float4*>(row + cs);
-            const float4* src4 = reinterpret_cast<const float4*>(seg);
-#pragma unroll
-            for (int i = 0; i < kSegFloats / 128; i++) {
-                const int vi = lane + 32 * i;
-                if (vi < nv) __stcs(dst4 + vi, src4[vi]);
+            if (lane == 0) {
+                const unsigned bytes = (unsigned)((ce - cs) * 4);
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(row + cs),
+                             "r"((unsigned)__cvta_generic_to_shared(seg)), "r"(bytes)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
-            __syncwarp();
-            for (int d = dstart + lane; d < dlo; d += 32) seg[emis[d] - cs] = CUDART_INF_F;
-            __syncwarp();
+            which ^= 1;
         }
         // tail scalars (at most 3 columns)
         {
@@ -1335,6 +1344,9 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
             }
         }
     }
+    // the buffers must outlive the stores that read them
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
 }
 
 // Deterministic reduction of the per-frame sums into two scalars (single block).
