@@ -39,8 +39,8 @@ SEQS_PER_GPU = {"triphone": 64, "bpe_ctc": 256, "monophone": 32, "ctc_tiny": 4, 
 CPU_SAMPLE_SEQS = None  # None: the full per-GPU batch of the workload
 
 # dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one triphone call divided by the
-# call's algorithmic bytes, from the ncu capture summarised in profiles/ (None until measured)
-TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# call's algorithmic bytes, from the ncu capture summarised in profiles/
+TRAFFIC_PER_ALGORITHMIC_BYTE = 0.89  # profiles/dram_traffic_triphone_b16.md (B=16 capture, scaled)
 
 
 def peaks():
