@@ -1924,4 +1924,136 @@ int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const
 
 int64_t fbw_b200_launch_count(void) { return (int64_t)g_launches.load(); }
 
+// ---------------------------------------------------------------------------------------------
+// The whole op without any caller-provided or allocated scratch
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory while they run: an inference server
+// whose memory pool is sized and frozen at start-up, or a component that is handed input and output
+// buffers by a framework and has no allocator of its own to ask for a plan and a work buffer.  For
+// them the plan and the run scratch live in one fixed array inside the library image.  Every GPU
+// that loads the library carries the array until the process exits, so it is kept modest: 64 MiB,
+// enough for the small and medium workloads (a 32-sequence, 500-frame monophone batch needs about
+// 45 MiB), not for the 1 GB of scratch of the large ones.
+constexpr size_t kNoAllocBytes = (size_t)64 << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+namespace {
+// In host code `g_noalloc_scratch` names a host-side shadow of the device array, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+std::mutex g_noalloc_mu;
+void*      g_noalloc_ptr[64]  = {nullptr};
+bool       g_noalloc_init[64] = {false};
+
+int noalloc_base(void** base) {
+    int dev = 0;
+    CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FBW_B200_BAD_ARGUMENT;
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_init[dev]) {
+        void* ptr = nullptr;
+        CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (!ptr) return FBW_B200_CUDA_ERROR;
+        g_noalloc_ptr[dev]  = ptr;
+        g_noalloc_init[dev] = true;
+    }
+    *base = g_noalloc_ptr[dev];
+    return FBW_B200_OK;
+}
+}  // namespace
+
+size_t fbw_b200_noalloc_capacity(void) { return kNoAllocBytes; }
+
+int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* weights,
+                         const int32_t* start_end, const int32_t* seq_lens, int64_t T, int64_t B,
+                         int64_t F, int64_t E, int64_t S, float* out, float* sums, float* loss2,
+                         fbw_b200_stream_t stream) {
+    if (!am || !out || !sums) return FBW_B200_BAD_ARGUMENT;
+    if (T <= 0 || B <= 0 || F <= 0 || S <= 0 || E < 0) return FBW_B200_BAD_ARGUMENT;
+    if (((uintptr_t)out & 15) != 0) return FBW_B200_BAD_ARGUMENT;
+    // calls at or above this size take the multi-stream pipeline, which creates streams and events
+    if ((double)T * (double)B * (double)F >= 1.0e8) return FBW_B200_TOO_LARGE;
+    void* base = nullptr;
+    int rc = noalloc_base(&base);  // first call on a device: looks the array's address up
+    if (rc != FBW_B200_OK) return rc;
+
+    // the plan at the front of the array, the run scratch behind it
+    const size_t plan_bytes = (plan_layout(B, E, S).total + 255) & ~(size_t)255;
+    if (plan_bytes > kNoAllocBytes) return FBW_B200_TOO_LARGE;
+    void* plan = base;
+    rc = prepare_impl(edges, weights, start_end, seq_lens, T, B, F, E, S, plan, plan_bytes, stream, true);
+    if (rc != FBW_B200_OK) return rc;
+    fbw_b200_summary sum;
+    rc = fbw_b200_plan_summary(plan, &sum, stream);  // synchronises the stream
+    if (rc == FBW_B200_RETRY_GENERAL) {
+        rc = prepare_impl(edges, weights, start_end, seq_lens, T, B, F, E, S, plan, plan_bytes, stream,
+                          false);
+        if (rc != FBW_B200_OK) return rc;
+        rc = fbw_b200_plan_summary(plan, &sum, stream);
+    }
+    if (rc != FBW_B200_OK) return rc;
+    const RunLayout R = run_layout(sum);
+    if (plan_bytes + R.total > kNoAllocBytes) return FBW_B200_TOO_LARGE;
+    void* work = static_cast<unsigned char*>(base) + plan_bytes;
+    const PlanLayout L = plan_layout(sum.B, sum.E, sum.S);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    RunArgs a;
+    a.am = am; a.out = out; a.sums = sums; a.loss2 = loss2;
+    a.A  = at<float>(work, R.A);
+    a.Bt = at<float>(work, R.Bt);
+    a.Gt = at<float>(work, R.Gt);
+    a.Gf = at<float>(work, R.Gf);
+    a.P  = at<float>(work, R.P);
+    a.X  = at<float>(work, R.X);
+    a.N  = at<float>(work, R.N);
+    a.carry  = at<float>(work, R.carry);
+    a.status = at<int>(work, R.status);
+    a.state_off = at<int>(plan, L.state_off);
+    a.edge_off  = at<int>(plan, L.edge_off);
+    a.slot_off  = at<int>(plan, L.slot_off);
+    a.nslot     = at<int>(plan, L.nslot);
+    a.seq_T     = at<int>(plan, L.seq_T);
+    a.start_l   = at<int>(plan, L.start_l);
+    a.end_l     = at<int>(plan, L.end_l);
+    a.ta_off = at<i64>(plan, L.ta_off);
+    a.tg_off = at<i64>(plan, L.tg_off);
+    a.gf_off = at<i64>(plan, L.gf_off);
+    a.gu_off = at<i64>(plan, L.gu_off);
+    a.pu_off = at<i64>(plan, L.pu_off);
+    a.tx_off = at<i64>(plan, L.tx_off);
+    a.m_pos  = at<int2>(plan, L.m_pos);
+    a.rowptr_f = at<int>(plan, L.rowptr_f);
+    a.rowptr_b = at<int>(plan, L.rowptr_b);
+    a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
+    a.bwd_rec  = at<uint2>(plan, L.bwd_rec);
+    a.q_rec    = at<int4>(plan, L.q_rec);
+    a.m_rec    = at<int4>(plan, L.m_rec);
+    a.m_ptr     = at<int>(plan, L.m_ptr);
+    a.slot_emis = at<int>(plan, L.slot_emis);
+    a.order     = at<int>(plan, L.order);
+    a.T = sum.T; a.B = sum.B; a.F = sum.F;
+    a.r0 = 0; a.r1 = (int)sum.B;
+    a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
+
+    // The array keeps whatever the previous call left in it.  The plan builder clears its own
+    // counters; here the two things of the run that must start at zero are cleared.
+    CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(sum.T * sum.B), st));
+    CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
+    i64 ms = 0, me = 0, md = 0;
+    for (int q = 0; q < FBW_B200_GROUPS; q++) {
+        ms = sum.group_max_states[q] > ms ? sum.group_max_states[q] : ms;
+        me = sum.group_max_edges[q] > me ? sum.group_max_edges[q] : me;
+        md = sum.group_max_slots[q] > md ? sum.group_max_slots[q] : md;
+    }
+    rc = launch_group(a, 0, (int)sum.B, ms, me, md, sum, st, nullptr, kDoAll);  // one stream, one chunk
+    if (rc != FBW_B200_OK) return rc;
+    if (loss2) {
+        k_loss<<<1, 1024, 0, st>>>(sums, sum.T, sum.B, loss2);
+        COUNT_LAUNCH(1);
+    }
+    CUDA_OK(cudaGetLastError());
+    return FBW_B200_OK;
+}
+
 }  // extern "C"

@@ -131,6 +131,28 @@ int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const
  * the CUB sort/scan kernels it calls during prepare).  No counterpart in the reference. */
 int64_t fbw_b200_launch_count(void);
 
+/* The whole op (prepare + summary + run) for callers that cannot allocate device memory while they
+ * run -- for example a server whose memory pool is fixed at start-up, or a plug-in that only ever
+ * receives input and output buffers from its host and has no allocator to ask for scratch.  The plan
+ * and the run scratch live in a fixed array inside the library (fbw_b200_noalloc_capacity() bytes,
+ * 64 MiB, held by every GPU that loads the library until the process exits).  Same inputs and
+ * outputs as fbw_b200_prepare + fbw_b200_run; loss2 may be NULL.  It has no counterpart in the
+ * reference, whose launcher allocates and frees per call (fbw_op.cu:283-286, 384-389).
+ *  - Returns FBW_B200_TOO_LARGE when plan + scratch exceed the capacity, or when T*B*F >= 1e8 (such
+ *    calls run as a multi-stream pipeline, which creates streams); nothing has run then.
+ *  - Calls no cudaMalloc/cudaFree and no allocating library routine.  SYNCHRONISES the stream once
+ *    (the host reads the plan summary).
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, that
+ *    device current); make that first call before any stream capture starts.
+ *  - All calls on a device share the one array: two calls that overlap on the GPU (different
+ *    streams or threads) race on it.  The array keeps the previous call's contents; everything a call
+ *    needs to start from zero it clears itself. */
+int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* weights,
+                         const int32_t* start_end, const int32_t* seq_lens, int64_t T, int64_t B,
+                         int64_t F, int64_t E, int64_t S, float* out, float* sums, float* loss2,
+                         fbw_b200_stream_t stream);
+size_t fbw_b200_noalloc_capacity(void);
+
 /* Text for a status code (static storage). */
 const char* fbw_b200_status_string(int status);
 
