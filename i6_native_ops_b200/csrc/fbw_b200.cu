@@ -1479,6 +1479,21 @@ StreamPool* stream_pool() {
     return p;
 }
 
+// number of size groups (1 or 8): only batches whose largest automaton is several times the average
+int choose_groups(const fbw_b200_summary& s) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("FBW_B200_NUM_GROUPS");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return s.B >= forced ? forced : 1;
+    if (s.B >= 64 && s.E > 0 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E &&
+        s.max_edges >= 2048) {
+        return 8;
+    }
+    return 1;
+}
+
 // number of time chunks of the pipeline: small calls run as one chunk on the caller's stream
 int choose_chunks(const fbw_b200_summary& s) {
     static int forced = -1;
@@ -1834,15 +1849,43 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     // beta are both known are scored, normalised and written out on a third stream while the sweeps
     // go on.  The sweeps are arithmetic-bound, the gather and the output pass memory-bound, so they
     // overlap well; only the first gather chunk and the last output chunk are exposed.
-    const int C = ev ? 1 : choose_chunks(s);
+    // Batches whose sequences differ a lot in size (lattices) run instead as size groups: rank
+    // ranges of the cost order, each launched with its own thread count and shared-memory size on
+    // its own stream, so that small automata do not inherit the footprint of the largest one and
+    // several of their CTAs share an SM.
+    const int G = ev ? 1 : choose_groups(s);
+    const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     i64 ms = 0, me = 0, md = 0;
     for (int q = 0; q < FBW_B200_GROUPS; q++) {
         ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
         me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
         md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
     }
-    StreamPool* pool = C > 1 ? stream_pool() : nullptr;
-    if (C > 1 && pool) {
+    StreamPool* pool = (C > 1 || G > 1) ? stream_pool() : nullptr;
+    if (G > 1 && pool) {
+        std::unique_lock<std::mutex> lock(pool->mu);
+        CUDA_OK(cudaEventRecord(pool->fork, st));
+        const int per = FBW_B200_GROUPS / G;  // base groups merged into one launch group
+        for (int g = 0; g < G; g++) {
+            const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
+            const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
+            if (r1 <= r0) continue;
+            i64 gs_ = 0, ge_ = 0, gd_ = 0;
+            for (int q = g * per; q < (g + 1) * per; q++) {
+                gs_ = s.group_max_states[q] > gs_ ? s.group_max_states[q] : gs_;
+                ge_ = s.group_max_edges[q] > ge_ ? s.group_max_edges[q] : ge_;
+                gd_ = s.group_max_slots[q] > gd_ ? s.group_max_slots[q] : gd_;
+            }
+            cudaStream_t gstream = g == 0 ? st : pool->aux[g];
+            if (g > 0) CUDA_OK(cudaStreamWaitEvent(gstream, pool->fork, 0));
+            int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll);
+            if (rc != FBW_B200_OK) return rc;
+            if (g > 0) {
+                CUDA_OK(cudaEventRecord(pool->join[g], gstream));
+                CUDA_OK(cudaStreamWaitEvent(st, pool->join[g], 0));
+            }
+        }
+    } else if (C > 1 && pool) {
         std::unique_lock<std::mutex> lock(pool->mu);
         a.chunk_steps = (int)(((s.max_len + C - 1) / C + kTile - 1) / kTile * kTile);
         const i64 J = a.chunk_steps;
