@@ -924,14 +924,14 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
         xi1  = i1;
 #pragma unroll
         for (int k = 0; k < kRegEdges; k++) {
-            const uint2 r = k < rcnt ? recs[i0 + k] : make_uint2(0u, 0u);
+            const uint2 r = k < rcnt ? recs[i0 + k] : make_uint2(0u, __float_as_uint(CUDART_INF_F));
             rfrom[k] = (int)(r.x & 0xffffu);
             rslot[k] = (int)(r.x >> 16);
-            rw[k]    = __uint_as_float(r.y);
+            rw[k]    = __uint_as_float(r.y);  // +inf for the entries past the state's edges
         }
     } else {
 #pragma unroll
-        for (int k = 0; k < kRegEdges; k++) { rfrom[k] = 0; rslot[k] = 0; rw[k] = 0.f; }
+        for (int k = 0; k < kRegEdges; k++) { rfrom[k] = 0; rslot[k] = 0; rw[k] = CUDART_INF_F; }
     }
 
     const float* __restrict__ gf = a.Gf + a.gf_off[b];
@@ -982,16 +982,15 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
                                       : gf + (i64)t * Dp;
             if (tid < Sb) {
+                // An unreachable source state (+inf) or a padding entry (weight +inf) gives +inf by
+                // itself, and prob_add treats +inf terms exactly (a + inf term leaves the sum as it
+                // is, a sum that is still +inf takes the term), so the register part needs no tests.
                 float v[kRegEdges];
 #pragma unroll
-                for (int k = 0; k < kRegEdges; k++) {
-                    const float pv = cur[rfrom[k]];
-                    const float gg = g[rslot[k]];
-                    v[k] = (k < rcnt && !isinf(pv)) ? (pv + rw[k]) + gg : CUDART_INF_F;
-                }
-                float acc = CUDART_INF_F;
+                for (int k = 0; k < kRegEdges; k++) v[k] = (cur[rfrom[k]] + rw[k]) + g[rslot[k]];
+                float acc = prob_first(v[0]);
 #pragma unroll
-                for (int k = 0; k < kRegEdges; k++) acc = prob_add_live(acc, v[k]);
+                for (int k = 1; k < kRegEdges; k++) acc = prob_add(acc, v[k]);
                 for (int i = xi0; i < xi1; i++) {
                     const uint2 r  = recs[i];
                     const float pv = cur[r.x & 0xffffu];
