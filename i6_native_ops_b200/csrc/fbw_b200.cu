@@ -1502,7 +1502,7 @@ int choose_chunks(const fbw_b200_summary& s) {
     }
     int C = 1;
     const double cells = (double)s.T * (double)s.B * (double)s.F;
-    if (cells >= 1.0e8 && s.max_len >= 512) C = 8;
+    if (cells >= 1.0e8 && s.max_len >= 512) C = 6;
     if (forced >= 1) C = forced;
     if (C > kMaxChunks) C = kMaxChunks;
     while (C > 1 && s.max_len / C < 2 * kTile) C--;  // at least two tiles per chunk
@@ -1897,28 +1897,36 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         CUDA_OK(cudaEventRecord(pool->fork, st));
         CUDA_OK(cudaStreamWaitEvent(gs, pool->fork, 0));
         for (int i = 1; i <= kPostStreams; i++) CUDA_OK(cudaStreamWaitEvent(pool->aux[i], pool->fork, 0));
+        // Enqueue stage by stage, not chunk by chunk: every gather first, then every sweep chunk,
+        // then the output stages.  The streams are independent queues, so the GPU sees the same
+        // dependencies, but the sweep chunks (the critical path) are all queued before the host
+        // spends time on the many small launches of the output stages.
+        for (int c = 0; c < C && c <= last_gather; c++) {
+            a.c_lo = c;
+            a.c_hi = c + 1;
+            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, gs, nullptr, kDoGather);
+            if (rc != FBW_B200_OK) return rc;
+            CUDA_OK(cudaEventRecord(pool->gathered[c], gs));
+        }
         for (int c = 0; c < C; c++) {
             a.c_lo = c;
             a.c_hi = c + 1;
-            int rc;
-            if (c <= last_gather) {
-                rc = launch_group(a, 0, (int)s.B, ms, me, md, s, gs, nullptr, kDoGather);
-                if (rc != FBW_B200_OK) return rc;
-                CUDA_OK(cudaEventRecord(pool->gathered[c], gs));
-                CUDA_OK(cudaStreamWaitEvent(st, pool->gathered[c], 0));
-            }
-            rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, nullptr, kDoSweep);
+            if (c <= last_gather) CUDA_OK(cudaStreamWaitEvent(st, pool->gathered[c], 0));
+            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, nullptr, kDoSweep);
             if (rc != FBW_B200_OK) return rc;
-            // the output stages of successive chunks go to different streams: each stage is a
-            // chain of latency-bound kernels, several chunks' chains have to be in flight at once
-            if (c == 0 || c >= first_finish) {
-                cudaStream_t ps = pool->aux[1 + c % kPostStreams];
-                CUDA_OK(cudaEventRecord(pool->swept[c], st));
-                CUDA_OK(cudaStreamWaitEvent(ps, pool->swept[c], 0));
-                rc = launch_group(a, 0, (int)s.B, ms, me, md, s, ps, nullptr,
+            if (c == 0 || c >= first_finish) CUDA_OK(cudaEventRecord(pool->swept[c], st));
+        }
+        // the output stages of successive chunks go to different streams: each stage is a chain
+        // of latency-bound kernels, several chunks' chains have to be in flight at once
+        for (int c = 0; c < C; c++) {
+            if (!(c == 0 || c >= first_finish)) continue;
+            a.c_lo = c;
+            a.c_hi = c + 1;
+            cudaStream_t ps = pool->aux[1 + c % kPostStreams];
+            CUDA_OK(cudaStreamWaitEvent(ps, pool->swept[c], 0));
+            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, ps, nullptr,
                                   c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
-                if (rc != FBW_B200_OK) return rc;
-            }
+            if (rc != FBW_B200_OK) return rc;
         }
         for (int i = 1; i <= kPostStreams; i++) {
             CUDA_OK(cudaEventRecord(pool->join[i], pool->aux[i]));
