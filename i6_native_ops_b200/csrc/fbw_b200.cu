@@ -1547,7 +1547,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         bool found = false;
         for (int es = 1; es >= 0 && !found; es--) {
             for (int tl = 1; tl >= 0 && !found; tl--) {
-                for (int rg = 8; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
+                for (int rg = 16; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
                     if (need(rg, tl, es) <= limit) {
                         ring = rg; tiled = tl; in_smem = es; found = true;
                     }
@@ -1562,6 +1562,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
     rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, (int)s.max_degree, st)
         if (tiled) {
             switch (ring) {
+                case 16: SWEEP_CASE(16, true); break;
                 case 8: SWEEP_CASE(8, true); break;
                 case 4: SWEEP_CASE(4, true); break;
                 case 2: SWEEP_CASE(2, true); break;
@@ -1569,6 +1570,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
             }
         } else {
             switch (ring) {
+                case 16: SWEEP_CASE(16, false); break;
                 case 8: SWEEP_CASE(8, false); break;
                 case 4: SWEEP_CASE(4, false); break;
                 case 2: SWEEP_CASE(2, false); break;
