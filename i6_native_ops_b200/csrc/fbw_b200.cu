@@ -768,6 +768,10 @@ struct RunArgs {
     // launch handles the chunks [c_lo, c_hi).  One chunk covering everything is the plain case.
     int c_lo, c_hi, chunk_steps;
     float* carry;  // state vectors handed from one sweep chunk to the next, [2 * state][direction]
+    // 1: the wrapper's passes are folded in -- `am` is log_probs (B,T,F) (sign and layout of the
+    // caller's tensor, i6_native_ops/fbw/__init__.py:66) and `out` receives the gradient with respect
+    // to it, -posterior in (B,T,F) with zeros elsewhere (what __init__.py:41-44 and autograd produce)
+    int fused;
 };
 
 // chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
@@ -822,12 +826,14 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
         for (int f = warp; f < kTile; f += 8) {
             const int  t     = k * kTile + f;
             const bool valid = t < Te;
-            const float* __restrict__ row = a.am + ((i64)t * B + b) * a.F;
+            const float* __restrict__ row =
+                a.am + (a.fused ? ((i64)b * a.T + t) : ((i64)t * B + b)) * a.F;
+            const float sgn = a.fused ? -1.f : 1.f;
             float v[kGatherSlots / 32];
 #pragma unroll
             for (int j = 0; j < kGatherSlots / 32; j++) {
                 int dd = lane + 32 * j;
-                v[j]   = (valid && dd < nd) ? __ldg(row + em[j]) : CUDART_INF_F;
+                v[j]   = (valid && dd < nd) ? sgn * __ldg(row + em[j]) : CUDART_INF_F;
             }
 #pragma unroll
             for (int j = 0; j < kGatherSlots / 32; j++) {
@@ -1251,6 +1257,11 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
     const int B = (int)a.B;
     const i64 F = a.F;
     int which = 0;  // segment buffer in use; the other one may still be read by a store in flight
+    // plain mode: background +inf, values are the negative log posteriors; fused mode: background 0,
+    // values are -posterior (the gradient with respect to log_probs)
+    const bool  fused = a.fused != 0;
+    const float bg    = fused ? 0.f : CUDART_INF_F;
+    auto pval = [&](float p) -> float { return fused ? -expf(-p) : p; };
     // Work item of a CTA: (32-frame tile, sequence), all T frames (frames past a sequence's length
     // are +inf rows).  A tile is written once the posteriors of its frames exist, i.e. in the chunk
     // after which both sweeps have passed it; tiles past the sequence's length go with chunk 0.
@@ -1269,7 +1280,7 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
         }
         const int  t  = k * kTile + qt * 8 + warp;
         if (t >= a.T) continue;
-        const i64  r  = (i64)t * B + b;
+        const i64  r  = a.fused ? (i64)b * a.T + t : (i64)t * B + b;
         const bool valid = t < a.seq_T[b];
         const int  so = a.slot_off[b];
         const int  Db = valid ? a.nslot[b] : 0;
@@ -1285,11 +1296,11 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
         int dlo = 0;  // next unconsumed slot; slots are in ascending emission id
         // head scalars
         if (head > 0) {
-            float v = CUDART_INF_F;
+            float v = bg;
             // at most 3 columns: the first slots may fall here
             for (int d = 0; d < Db && d < 3; d++) {
                 int e = emis[d];
-                if (e == lane && e < head) v = Pr[d];
+                if (e == lane && e < head) v = pval(Pr[d]);
             }
             if (lane < head) row[lane] = v;
             while (dlo < Db && emis[dlo] < head) dlo++;
@@ -1304,7 +1315,7 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
             {
-                const float4 inf4 = make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F);
+                const float4 inf4 = make_float4(bg, bg, bg, bg);
                 float4* s4 = reinterpret_cast<float4*>(seg);
 #pragma unroll
                 for (int i = 0; i < kSegFloats / 128; i++) s4[lane + 32 * i] = inf4;
@@ -1315,7 +1326,7 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
                 const int d  = dlo + lane;
                 const int e  = d < Db ? emis[d] : 0x7fffffff;
                 const bool in = e < ce;
-                if (in) seg[e - cs] = Pr[d];
+                if (in) seg[e - cs] = pval(Pr[d]);
                 n = __popc(__ballot_sync(0xffffffffu, in));
                 dlo += n;
             } while (n == 32);
@@ -1335,9 +1346,9 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
         {
             const int ntail = (int)(F - body_end);
             if (ntail > 0) {
-                float v = CUDART_INF_F;
+                float v = bg;
                 for (int d = dlo; d < Db; d++) {
-                    if (emis[d] - body_end == lane) v = Pr[d];
+                    if (emis[d] - body_end == lane) v = pval(Pr[d]);
                 }
                 if (lane < ntail) row[body_end + lane] = v;
             }
@@ -1792,7 +1803,7 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
 
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
-                    fbw_b200_stream_t stream, cudaEvent_t* ev) {
+                    fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0) {
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -1839,6 +1850,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.T = s.T; a.B = s.B; a.F = s.F;
     a.r0 = 0; a.r1 = (int)s.B;
     a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
+    a.fused = fused;
 
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
@@ -1952,6 +1964,12 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
                  float* sums, float* loss2, void* work, size_t work_bytes,
                  fbw_b200_stream_t stream) {
     return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr);
+}
+
+int fbw_b200_run_fused(const void* plan, const fbw_b200_summary* summary, const float* log_probs,
+                       float* grad, float* sums, float* loss2, void* work, size_t work_bytes,
+                       fbw_b200_stream_t stream) {
+    return run_impl(plan, summary, log_probs, grad, sums, loss2, work, work_bytes, stream, nullptr, 1);
 }
 
 int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,
@@ -2087,6 +2105,7 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
     a.T = sum.T; a.B = sum.B; a.F = sum.F;
     a.r0 = 0; a.r1 = (int)sum.B;
     a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
+    a.fused = 0;
 
     // The array keeps whatever the previous call left in it.  The plan builder clears its own
     // counters; here the two things of the run that must start at zero are cleared.

@@ -144,6 +144,31 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
     return run_impl(p, am_scores, false, out, sums);
 }
 
+// The op with the wrapper's passes folded in: log_probs (B,T,F) as the caller holds them ->
+// [grad (B,T,F) = -posterior, sum_output (T,B)].  Replaces neg/transpose/contiguous before the op
+// and neg/exp after it (i6_native_ops/fbw/__init__.py:41-44, 66); opt-in, used by fbw_loss_fused.
+std::vector<torch::Tensor> fbw_fused(torch::Tensor& log_probs, torch::Tensor& edges,
+                                     torch::Tensor& weights, torch::Tensor& start_end_states,
+                                     torch::Tensor& seq_lens, int64_t num_states) {
+    check_input(log_probs, torch::kFloat32, "log_probs");
+    TORCH_CHECK(log_probs.dim() == 3, "log_probs must have shape (B, T, F)");
+    TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == log_probs.size(0),
+                "start_end_states must have shape (2, B) with B = log_probs.size(0)");
+    c10::cuda::CUDAGuard guard(log_probs.device());
+    const int64_t B = log_probs.size(0), T = log_probs.size(1), F = log_probs.size(2);
+    torch::Tensor grad = torch::empty_like(log_probs);
+    torch::Tensor sums = torch::empty({T, B}, log_probs.options());
+    Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, T, F, num_states);
+    auto stream = at::cuda::getCurrentCUDAStream();
+    size_t wbytes = fbw_b200_run_bytes(&p.summary);
+    torch::Tensor work = byte_buffer(wbytes, log_probs.device());
+    check_status(fbw_b200_run_fused(p.plan.data_ptr(), &p.summary, log_probs.data_ptr<float>(),
+                                    grad.data_ptr<float>(), sums.data_ptr<float>(), nullptr,
+                                    work.data_ptr(), wbytes,
+                                    reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    return {grad, sums};
+}
+
 // Two-step form of the same op for callers that reuse one batch of automata with new scores:
 // fbw_prepare(...) -> opaque handle, fbw_run(handle, am_scores) -> [out, sum_output, loss2].
 // loss2 = [sum of sum_output, sum over sequences of sum_output[0]].
@@ -215,6 +240,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fbw_run_phases", &fbw_run_phases, "fbw_run with per-kernel device times");
     m.def("launch_count", []() { return fbw_b200_launch_count(); });
     m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");
+    m.def("fbw_fused", &fbw_fused, "fbw on (B,T,F) log_probs, returning the gradient directly");
     m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
     m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
     m.def("abi_version", []() { return fbw_b200_abi_version(); });

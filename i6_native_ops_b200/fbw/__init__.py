@@ -80,4 +80,29 @@ def fbw_loss(
     return FastBaumWelchLoss.apply(neg_log_probs, fsa, seq_lens)
 
 
-__all__ = ["core", "FastBaumWelchLoss", "fbw_loss"]
+class FusedFastBaumWelchLoss(torch.autograd.Function):
+    """``apply(log_probs (B,T,F), fsa, seq_lens) -> (T,B)`` per-frame sums, with the wrapper's
+    elementwise passes done inside the kernels: the op reads ``log_probs`` in place (no negated,
+    transposed copy) and writes ``d loss.sum() / d log_probs = -posterior`` directly in (B,T,F).
+    Like the reference's backward it does not scale by the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, log_probs, fsa, seq_lens):
+        num_states, edge_tensor, weight_tensor, start_end_states = fsa
+        grad, loss = core.fbw_fused(log_probs, edge_tensor, weight_tensor, start_end_states,
+                                    seq_lens, int(num_states))
+        ctx.save_for_backward(grad)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        return ctx.saved_tensors[0], None, None
+
+
+def fbw_loss_fused(log_probs, fsa, seq_lens):
+    """Same result and gradient as :func:`fbw_loss` (opt-in): four passes over the (B,T,F) tensor
+    fewer per training step.  ``log_probs`` must be a contiguous float32 CUDA tensor."""
+    return FusedFastBaumWelchLoss.apply(log_probs.contiguous(), fsa, seq_lens)
+
+
+__all__ = ["core", "FastBaumWelchLoss", "fbw_loss", "FusedFastBaumWelchLoss", "fbw_loss_fused"]

@@ -117,6 +117,15 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
                  float* sums, float* loss2, void* work, size_t work_bytes,
                  fbw_b200_stream_t stream);
 
+/* fbw_b200_run with the Python wrapper's elementwise passes folded in (the steps either side of the
+ * op in i6_native_ops/fbw/__init__.py:41-44 and :66): the input is log_probs in the caller's own
+ * (B,T,F) layout and sign (prepare was given T, B, F of that tensor), the output `grad` (B,T,F) is
+ * d(sum of sums)/d(log_probs) = -posterior, 0 where the posterior is 0 and for t >= seq_len.  `sums`
+ * (T,B) and loss2 as in fbw_b200_run.  Saves four passes over the (B,T,F) tensor per training step. */
+int fbw_b200_run_fused(const void* plan, const fbw_b200_summary* summary, const float* log_probs,
+                       float* grad, float* sums, float* loss2, void* work, size_t work_bytes,
+                       fbw_b200_stream_t stream);
+
 /* fbw_b200_run with per-phase device timing, for benchmarks and profiles: same arguments and
  * results, plus phase_ms (HOST, FBW_B200_NUM_PHASES floats) = milliseconds of the gather, sweep,
  * posterior, expand and loss-reduction kernels measured with CUDA events on `stream`.

@@ -310,3 +310,27 @@ def test_full_size_triphone_properties(fbw_mod, ref_core, cuda):
         assert rec["post_vs_ref"] <= max(POST_ATOL, 2 * rec["ref_vs_ref_post"])
     else:
         report("triphone_full", **rec)
+
+
+@pytest.mark.parametrize("name,kw", [("ctc_tiny", dict()), ("monophone", dict(B=6, T=180, scale=0.3)),
+                                     ("triphone", dict(B=20, T=600, F=4001, scale=0.4))])
+def test_fused_wrapper_matches_plain_wrapper(fbw_mod, cuda, name, kw):
+    """fbw_loss_fused folds the wrapper's passes (i6_native_ops/fbw/__init__.py:41-44, 66) into
+    the kernels: same (T,B) loss, same gradient -posterior in (B,T,F)."""
+    b = wl.make_batch(name, **kw)
+    am = wl.make_scores(b, cuda)
+    fsa, sl = wl.to_torch(b, cuda)
+    lp1 = (-am).transpose(0, 1).contiguous().requires_grad_(True)  # (B,T,F) log probs
+    lp2 = lp1.detach().clone().requires_grad_(True)
+    loss1 = fbw_mod.fbw_loss(lp1, fsa, sl)
+    loss1.sum().backward()
+    loss2 = fbw_mod.fbw_loss_fused(lp2, fsa, sl)
+    loss2.sum().backward()
+    assert torch.equal(loss1, loss2)
+    assert float((lp1.grad - lp2.grad).abs().max()) <= 1e-6
+    t = torch.arange(b.T, device=cuda)[None, :, None]
+    pad = (t >= sl[:, None, None]).expand_as(lp2.grad)
+    assert bool((lp2.grad[pad] == 0).all())
+    rows = -lp2.grad.sum(-1)
+    valid = (torch.arange(b.T, device=cuda)[None, :] < sl[:, None])
+    assert float((rows[valid] - 1).abs().max()) < 5e-3
