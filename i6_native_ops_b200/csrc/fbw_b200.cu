@@ -46,7 +46,7 @@ namespace {
 
 constexpr int kTile        = 32;   // frames per tile of the tiled layouts (= one lane per frame)
 constexpr int kGatherSlots = 256;  // classes per gather work item
-constexpr int kSegFloats   = 256;  // floats per output segment composed in shared memory
+constexpr int kSegFloats   = 512;  // floats per output segment composed in shared memory
 constexpr int kMaxPerSeq   = 65535;
 
 typedef long long i64;
@@ -1028,52 +1028,6 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
         }
     }
     if (RING > 0) cp_async_wait<0>();
-}
-
-// ---- bulk-copy (TMA) helpers: 1-D cp.async.bulk global -> shared, completion on an mbarrier ----
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// both addresses 16-byte aligned, bytes a multiple of 16
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
-                                         unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-        : "memory");
-}
-
-// named barriers (ids 1..15; 0 is __syncthreads): sync waits, arrive only signals
-// The id is an immediate so that the compiler can count the barriers a CTA really uses (a register
-// id makes it reserve all 16, which caps the resident CTAs per SM).
-template <int ID>
-__device__ __forceinline__ void named_sync(int count) {
-    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(count) : "memory");
-}
-template <int ID>
-__device__ __forceinline__ void named_arrive(int count) {
-    asm volatile("bar.arrive %0, %1;" ::"n"(ID), "r"(count) : "memory");
 }
 
 constexpr int kPostBatch = 8;  // edges whose lines are loaded together
