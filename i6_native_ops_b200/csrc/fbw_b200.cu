@@ -40,6 +40,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace {
@@ -815,7 +816,7 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
         const int nd = min(kGatherSlots, Db - d0);
         const int* __restrict__ emis = a.slot_emis + so + d0;
         float* __restrict__ gf = a.Gf + a.gf_off[b];
-        float* __restrict__ gt = a.Gt + a.tg_off[b] + ((i64)k * Db + d0) * kTile;
+        float* __restrict__ gt = a.Gt ? a.Gt + a.tg_off[b] + ((i64)k * Db + d0) * kTile : nullptr;
 
         int em[kGatherSlots / 32];
 #pragma unroll
@@ -828,7 +829,7 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
             const bool valid = t < Te;
             const float* __restrict__ row =
                 a.am + (a.fused ? ((i64)b * a.T + t) : ((i64)t * B + b)) * a.F;
-            const float sgn = a.fused ? -1.f : 1.f;
+            const float sgn = a.fused == 1 ? -1.f : 1.f;  // 2: batch-major input, sign kept
             float v[kGatherSlots / 32];
 #pragma unroll
             for (int j = 0; j < kGatherSlots / 32; j++) {
@@ -848,7 +849,9 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
             }
         }
         __syncthreads();
-        for (int dd = warp; dd < nd; dd += 8) gt[(i64)dd * kTile + lane] = tile[lane][dd];
+        if (gt) {
+            for (int dd = warp; dd < nd; dd += 8) gt[(i64)dd * kTile + lane] = tile[lane][dd];
+        }
         __syncthreads();
     }
 }
@@ -1571,7 +1574,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
 
 extern "C" {
 
-int fbw_b200_abi_version(void) { return 1; }
+int fbw_b200_abi_version(void) { return 2; }
 
 const char* fbw_b200_status_string(int status) {
     switch (status) {
@@ -2082,3 +2085,5 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
 }
 
 }  // extern "C"
+
+#include "viterbi_b200.inc"

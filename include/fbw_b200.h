@@ -126,6 +126,24 @@ int fbw_b200_run_fused(const void* plan, const fbw_b200_summary* summary, const 
                        float* grad, float* sums, float* loss2, void* work, size_t work_bytes,
                        fbw_b200_stream_t stream);
 
+/* Best-path (Viterbi) alignment on the same plan: replaces the reference's second FSA op,
+ * fast_viterbi_cuda()  (i6_native_ops/fast_viterbi/core.cu:174-275), which its binding
+ * fast_viterbi()  (i6_native_ops/fast_viterbi/binding.cpp:13-25) calls with the same five arrays.
+ * `scores_in` holds POSITIVE log scores (larger is better), (T,B,F) f32.  Outputs, as core.cu:274:
+ * `alignment` (T,B) i32 = emission id of the best path's edge at each frame, 0 for frames
+ * t >= seq_len and where no edge was recorded; `scores` (B) f32 = value of the best path ending
+ * in the end state after seq_len frames (-inf if there is none).  Ties are broken as in the
+ * reference (core.cu:37-40): the smaller edge index wins, so alignment and scores are reproduced
+ * bit for bit.  A seq_len outside [0, T] (the reference then reads past its table) is treated as 0.
+ * batch_major != 0 folds in the wrapper's two transposes (i6_native_ops/fast_viterbi/__init__.py:37,
+ * 46): `scores_in` is the caller's (B,T,F) log_probs and `alignment` is written as (B,T).
+ * The plan is the one fbw_b200_prepare builds (same automata, same seq_lens); `work` needs
+ * fbw_b200_viterbi_bytes(summary) bytes, 256-byte aligned.  Enqueues on `stream`, no synchronisation. */
+size_t fbw_b200_viterbi_bytes(const fbw_b200_summary* summary);
+int fbw_b200_viterbi(const void* plan, const fbw_b200_summary* summary, const float* scores_in,
+                     int32_t* alignment, float* scores, int batch_major, void* work,
+                     size_t work_bytes, fbw_b200_stream_t stream);
+
 /* fbw_b200_run with per-phase device timing, for benchmarks and profiles: same arguments and
  * results, plus phase_ms (HOST, FBW_B200_NUM_PHASES floats) = milliseconds of the gather, sweep,
  * posterior, expand and loss-reduction kernels measured with CUDA events on `stream`.

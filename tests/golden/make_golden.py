@@ -5,7 +5,11 @@ from the reference's own sources).  For each small seeded case it stores the inp
 reference's two outputs (fbw_op.cu:392) in one .npz.  The oracle and the CUDA path are both
 tested against these files.
 
-Usage:  python tests/golden/make_golden.py [output_dir]
+``--viterbi`` instead reads the inputs of the existing fixtures and stores, per case, what the
+REFERENCE fast_viterbi op (core.cu:274) returns for the positive log scores ``-am`` in
+``viterbi_<case>.npz`` (alignment (T,B) int32, scores (B,) float32); the fbw fixtures stay untouched.
+
+Usage:  python tests/golden/make_golden.py [--viterbi] [output_dir]
 """
 import os
 import sys
@@ -59,5 +63,24 @@ def main(out_dir):
         print(key, c["am"].shape, float(sums.max()))
 
 
+def main_viterbi(out_dir):
+    ref = build_ref.load_viterbi_ref()
+    if ref is None:
+        raise SystemExit("reference fast_viterbi op not built: run oracle/build_ref.py where the reference is mounted")
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    os.makedirs(out_dir, exist_ok=True)
+    for key in ["reference_unit_test"] + list(CASES):
+        c = np.load(os.path.join(HERE, key + ".npz"))
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        alignment, scores = ref.fast_viterbi(t(-c["am"]), t(c["edges"]), t(c["weights"]), t(c["start_end"]),
+                                             t(c["seq_lens"]), int(c["num_states"]))
+        torch.cuda.synchronize()
+        np.savez_compressed(os.path.join(out_dir, "viterbi_" + key + ".npz"),
+                            ref_alignment=alignment.cpu().numpy(), ref_scores=scores.cpu().numpy())
+        print(key, alignment.shape, scores.cpu().numpy()[:4])
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else HERE)
+    args = [a for a in sys.argv[1:] if a != "--viterbi"]
+    (main_viterbi if "--viterbi" in sys.argv else main)(args[0] if args else HERE)
