@@ -18,6 +18,10 @@ Printed by rank 0: ONE JSON line.
              CPU implementation of fbw) on a bounded sample of the same workload
 
 --impl reference times that CPU port alone (the reference's op is CUDA-only and has no CPU path).
+
+--op viterbi benchmarks the best-path alignment (fast_viterbi) on the same workloads instead: one
+step = automaton preparation + gather + the per-sequence Viterbi kernel (all frames and the
+back-trace); value = frames/s, e2e with host buffers, cpu_baseline = the sequential C oracle.
 """
 from __future__ import annotations
 
@@ -170,6 +174,182 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_viterbi(args):
+    """--op viterbi: the best-path alignment on the same synthetic workloads (positive log scores =
+    minus the fbw scores).  Sequences are independent: with N GPUs every rank aligns its own
+    sequences and nothing crosses GPUs."""
+    import oracle  # noqa: F401  (only the cpu_baseline leg below calls it)
+    from i6_native_ops_b200 import workloads as wl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    per_gpu = args.seqs_per_gpu or SEQS_PER_GPU[args.workload]
+
+    def cpu_pass(passes):
+        batch = wl.make_batch(args.workload, B=per_gpu)
+        am = -wl.make_scores(batch, "cpu").numpy()
+        times = []
+        for i in range(passes + 1):
+            t0 = time.perf_counter()
+            oracle.viterbi_oracle(am, batch.edges, batch.weights, batch.start_end, batch.seq_lens,
+                                  batch.num_states)
+            if i:
+                times.append(time.perf_counter() - t0)
+        sample = (f"{batch.B} sequences of {args.workload} at full T={batch.T}, F={batch.F}; sequential C "
+                  f"port of the reference arithmetic, {passes} passes")
+        return batch.T * batch.B * len(times) / float(sum(times)), sample
+
+    if args.impl == "reference":  # the reference op is CUDA-only: its arithmetic on one host core
+        if rank == 0:
+            value, sample = cpu_pass(max(1, args.steps))
+            print(json.dumps({
+                "impl": "reference", "metric": "viterbi frames/s", "value": value, "unit": "frames/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload, "op": "viterbi", "sample": sample},
+                "cpu_baseline": {"value": value, "unit": "frames/s", "cores": 1, "kind": "port", "sample": sample},
+                "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}), flush=True)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from i6_native_ops_b200 import sharding
+    from i6_native_ops_b200.fast_viterbi import core
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    global_b = per_gpu * world
+    if world > 1:
+        full = wl.make_batch(args.workload, B=global_b)
+        costs = sharding.sequence_costs(full.states_per_seq, full.edges_per_seq, full.seq_lens, full.T, full.F)
+        batch = wl.make_batch(args.workload, seq_ids=sharding.partition(costs, world)[rank], T=full.T)
+    else:
+        batch = wl.make_batch(args.workload, B=global_b)
+    am = wl.make_scores(batch, dev).neg_()
+    fsa, seq_lens = wl.to_torch(batch, dev)
+    S = int(fsa[0])
+    frames, alg_bytes = batch.T * batch.B, batch.viterbi_algorithmic_bytes()
+    am_bytes = am.numel() * 4
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device=dev) if am_bytes <= 2 * 126e6 else None
+
+    def step():
+        return core.fast_viterbi(am, fsa[1], fsa[2], fsa[3], seq_lens, S)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    clk = ClockSampler(local_rank).start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = core.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.time()
+    ms = 0.0
+    if flush is None:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+    else:
+        for _ in range(args.steps):
+            flush.fill_(1.0)
+            ev0.record()
+            step()
+            ev1.record()
+            torch.cuda.synchronize()
+            ms += ev0.elapsed_time(ev1)
+    barrier()
+    clk.window(w0, time.time())
+    clk.stop()
+    launches = core.launch_count() - launches0
+    t_ms = torch.tensor([ms], device=dev, dtype=torch.float64)
+    tot = torch.tensor([float(frames)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    ms_per_step = float(t_ms.item()) / args.steps
+    value = float(tot.item()) / (ms_per_step * 1e-3)
+
+    e2e = None
+    if not args.no_e2e:
+        am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
+        am_h.copy_(am)
+        host_fsa = [t.cpu().pin_memory() for t in (fsa[1], fsa[2], fsa[3], seq_lens)]
+        align_h = torch.empty((batch.T, batch.B), dtype=torch.int32, pin_memory=True)
+        am_d = torch.empty_like(am)
+        del am
+        h2d = am_h.numel() * 4 + sum(t.numel() * t.element_size() for t in host_fsa)
+        d2h = align_h.numel() * 4 + 4 * batch.B
+
+        def e2e_step():
+            am_d.copy_(am_h, non_blocking=True)
+            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
+            alignment, scores = core.fast_viterbi(am_d, e_, w_, se_, sl_, S)
+            align_h.copy_(alignment, non_blocking=True)
+            return scores.cpu()  # device -> host read of the scores; synchronises
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        ev0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        ev1.record()
+        barrier()
+        t_e = torch.tensor([ev0.elapsed_time(ev1) / n_e2e], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+        e2e = {"value": float(tot.item()) / (float(t_e.item()) * 1e-3), "unit": "frames/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": float(t_e.item()), "steps": n_e2e}
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": "viterbi frames/s", "value": value, "unit": "frames/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "op": "viterbi", "T": batch.T, "B_per_gpu": batch.B,
+                       "B_global": global_b, "F": batch.F, "edges_per_gpu": batch.num_edges,
+                       "states_per_gpu": batch.num_states, "partition": "by sequence, length-balanced",
+                       "l2": f"inputs ({am_bytes / 1e9:.2f} GB of scores per call) exceed the 126 MB L2; no flush"
+                             if am_bytes > 2 * 126e6 else "an L2 flush (256 MB write) runs between timed steps",
+                       "step": "prepare + gather + Viterbi kernel per call (automata re-sorted every step)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_call": int(alg_bytes),
+                         "scope": "whole op call (all kernels), per GPU; the frame recursion is a "
+                                  "dependent chain, not a bandwidth-bound pass"},
+            "gpu_launches": int(launches),
+            "clocks": clk.summary(),
+            "e2e": e2e,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cvalue, sample = cpu_pass(2)
+            line["cpu_baseline"] = {"value": cvalue, "unit": "frames/s", "cores": 1, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -180,9 +360,13 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--op", default="fbw", choices=["fbw", "viterbi"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
+    if args.op == "viterbi":
+        run_viterbi(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return

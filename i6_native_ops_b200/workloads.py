@@ -54,6 +54,17 @@ class FbwBatch:
         ts = int((self.seq_lens.astype(np.int64).clip(0, self.T) * self.states_per_seq).sum())
         return 2 * tbf + 8 * ts + 4 * self.T * self.B
 
+    def viterbi_algorithmic_bytes(self) -> int:
+        """Bytes one best-path call must move: one 32-byte DRAM sector per score it needs (a
+        distinct (frame, sequence, emission) triple; scores of one emission in adjacent frames lie
+        B*F*4 bytes apart, so no two share a sector), the back-pointers of every valid frame written
+        once and read once, and the (T,B) alignment plus the (B,) scores."""
+        lens = self.seq_lens.astype(np.int64).clip(0, self.T)
+        pairs = np.unique(self.edges[3].astype(np.int64) * self.F + self.edges[2].astype(np.int64))
+        distinct = np.bincount(pairs // self.F, minlength=self.B)  # emissions per sequence
+        ts = int((lens * self.states_per_seq).sum())
+        return 32 * int((lens * distinct).sum()) + 8 * ts + 4 * self.T * self.B + 4 * self.B
+
 
 # ----------------------------------------------------------------------------------------------
 # per-sequence automaton builders; each returns (n_states, from, to, emission, weight, start, end)
