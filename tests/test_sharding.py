@@ -44,6 +44,19 @@ def test_extract_shard_matches_full_batch():
         assert np.array_equal(o, out[:, idx])
 
 
+def test_extract_shard_matches_full_batch_viterbi():
+    """The best-path alignment shards the same way and needs no collective at all."""
+    b = wl.make_batch("lattice", B=7, F=40, T=120, scale=0.06, shuffle_edges=True)
+    am = -wl.make_scores(b).numpy()
+    alignment, scores = oracle.viterbi_oracle(am, b.edges, b.weights, b.start_end, b.seq_lens, b.num_states)
+    costs = sharding.sequence_costs(b.states_per_seq, b.edges_per_seq, b.seq_lens, b.T, b.F)
+    for idx in sharding.partition(costs, 2):
+        S, e, w, se, sl = sharding.extract_shard(b.num_states, b.edges, b.weights, b.start_end,
+                                                 b.seq_lens, idx)
+        a, s_ = oracle.viterbi_oracle(am[:, idx], e, w, se, sl, S)
+        assert np.array_equal(a, alignment[:, idx]) and np.array_equal(s_, scores[idx])
+
+
 def test_shards_generated_independently_match_the_full_batch():
     """Per-sequence seeding: a rank that builds only its own sequences gets the same automata."""
     full = wl.make_batch("monophone", B=6, T=150, scale=0.3)
