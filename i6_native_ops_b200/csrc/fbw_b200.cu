@@ -2086,4 +2086,60 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
 
 }  // extern "C"
 
+// ---------------------------------------------------------------------------------------------
+// debug export: the forward state scores of the last run, dense and indexed by global state id
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// thread per (frame, global state); consecutive threads walk the states of one frame, so the
+// (T,S) destination is written coalesced
+__global__ void k_export_alpha(const float* __restrict__ A, const int* __restrict__ state_key,
+                               const int* __restrict__ packed_of, const int* __restrict__ state_off,
+                               const int* __restrict__ seq_T, const int* __restrict__ start_l,
+                               const i64* __restrict__ ta_off, i64 T, i64 S, float* __restrict__ dst) {
+    const i64 n = T * S;
+    for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
+        const int t = (int)(i / S);
+        const int g = (int)(i - (i64)t * S);
+        const int q = state_key[g];
+        float v = CUDART_INF_F;
+        if (q >= 0) {
+            const int s0 = state_off[q], Sb = state_off[q + 1] - s0;
+            const int l  = packed_of[g] - s0;
+            const int Te = seq_T[q];
+            if (t < Te) {
+                v = A[ta_off[q] + ((i64)(t >> 5) * Sb + l) * kTile + (t & 31)];
+            } else if (t == 0) {
+                v = l == start_l[q] ? 0.f : CUDART_INF_F;  // the initial vector (fbw_op.cu:297-302)
+            }
+        }
+        dst[i] = v;
+    }
+}
+
+}  // namespace
+
+extern "C" int fbw_b200_export_alpha(const void* plan, const fbw_b200_summary* summary,
+                                     const void* work, size_t work_bytes, float* alpha,
+                                     fbw_b200_stream_t stream) {
+    if (!plan || !summary || !work || !alpha) return FBW_B200_BAD_ARGUMENT;
+    if (summary->error) return FBW_B200_BAD_AUTOMATON;
+    const fbw_b200_summary& s = *summary;
+    const RunLayout R = run_layout(s);
+    if (work_bytes < R.total) return FBW_B200_WORKSPACE;
+    const PlanLayout L = plan_layout(s.B, s.E, s.S);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const i64 n = s.T * s.S;
+    i64 blocks = (n + 255) / 256;
+    const i64 cap = (i64)sm_count() * 16;
+    k_export_alpha<<<(int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap), 256, 0, st>>>(
+        at<float>(work, R.A), at<int>(plan, L.state_key),
+        at<int>(plan, L.packed_of), at<int>(plan, L.state_off),
+        at<int>(plan, L.seq_T), at<int>(plan, L.start_l),
+        at<i64>(plan, L.ta_off), s.T, s.S, alpha);
+    COUNT_LAUNCH(1);
+    CUDA_OK(cudaGetLastError());
+    return FBW_B200_OK;
+}
+
 #include "viterbi_b200.inc"

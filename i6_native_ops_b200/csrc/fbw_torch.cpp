@@ -1,7 +1,8 @@
 // fbw_torch.cpp -- torch extension `fbw_core`: the Python-visible op over the C ABI of
 // include/fbw_b200.h.  Mirrors the reference binding i6_native_ops/fbw/fbw_torch.cpp:15-40:
 // same module members (`fbw`, `DebugOptions`), same seven positional arguments, same input
-// checks (CUDA, contiguous, dtype -> RuntimeError), same two outputs.
+// checks (CUDA, contiguous, dtype -> RuntimeError), same two outputs, same text dumps under
+// DebugOptions.
 //
 // Differences that do not change results: scratch comes from torch's caching allocator instead
 // of cudaMalloc/cudaFree per call (fbw_op.cu:283-286, 384-389); work is enqueued on torch's current
@@ -12,6 +13,11 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <atomic>
+#include <cmath>
+#include <fstream>
+#include <limits>
+#include <sstream>
 #include <vector>
 
 #include "fbw_b200.h"
@@ -37,7 +43,8 @@ namespace {
 
 std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_scores,
                                     bool want_loss, torch::Tensor out = torch::Tensor(),
-                                    torch::Tensor sums = torch::Tensor()) {
+                                    torch::Tensor sums = torch::Tensor(),
+                                    torch::Tensor* work_out = nullptr) {
     auto stream = at::cuda::getCurrentCUDAStream();
     const fbw_b200_summary& s = p.summary;
     if (!out.defined()) out = torch::empty_like(am_scores);
@@ -50,8 +57,63 @@ std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_s
                               out.data_ptr<float>(), sums.data_ptr<float>(),
                               want_loss ? loss2.data_ptr<float>() : nullptr, work.data_ptr(),
                               wbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    if (work_out) *work_out = work;
     if (want_loss) return {out, sums, loss2};
     return {out, sums};
+}
+
+// The reference's text dumps (fbw_op.cu:155-224), written into the current directory like there.
+// alignment.dump.<call>.<seq>: per frame t < seq_len (frame 0 always) the forward state scores of the
+// states start..end of the sequence, normalised over those states, one line "t local_state value" for
+// every value <= pruning.  target.dump.<call>.<seq>: per frame the output values <= pruning, one line
+// "t emission value".  Values are printed by a default-formatted ostream (6 significant digits).
+void write_alignment_dump(const torch::Tensor& alpha_dev, const torch::Tensor& start_end_states,
+                          const torch::Tensor& seq_lens, float pruning, unsigned call_idx) {
+    torch::Tensor alpha = alpha_dev.cpu();
+    torch::Tensor se = start_end_states.cpu(), sl = seq_lens.cpu();
+    const int64_t T = alpha.size(0), S = alpha.size(1), B = sl.size(0);
+    const float*   a    = alpha.data_ptr<float>();
+    const int32_t* sep  = se.data_ptr<int32_t>();
+    const int32_t* lens = sl.data_ptr<int32_t>();
+    for (int64_t b = 0; b < B; b++) {
+        std::ostringstream name;
+        name << "alignment.dump." << call_idx << '.' << b;
+        std::ofstream f(name.str().c_str(), std::ios::out | std::ios::trunc);
+        const int64_t first = sep[b], last = sep[B + b];
+        const uint32_t len = (uint32_t)lens[b];  // the reference keeps lengths unsigned
+        for (int64_t t = 0; t < T && !(t > 0 && (uint64_t)t >= len); t++) {
+            const float* row = a + t * S;
+            float total = std::numeric_limits<float>::infinity();
+            for (int64_t s = first; s <= last; s++) {
+                const float d = row[s] - total;
+                if (!std::isnan(d)) total = -log1pf(expf(-fabsf(d))) + fminf(total, row[s]);
+            }
+            for (int64_t s = first; s <= last; s++) {
+                const float v = row[s] - total;
+                if (v <= pruning) f << t << ' ' << (s - first) << ' ' << v << '\n';
+            }
+        }
+    }
+}
+
+void write_output_dump(const torch::Tensor& out_dev, const torch::Tensor& seq_lens, float pruning,
+                       unsigned call_idx) {
+    torch::Tensor out = out_dev.cpu(), sl = seq_lens.cpu();
+    const int64_t T = out.size(0), B = out.size(1), F = out.size(2);
+    const float*   o    = out.data_ptr<float>();
+    const int32_t* lens = sl.data_ptr<int32_t>();
+    for (int64_t b = 0; b < B; b++) {
+        std::ostringstream name;
+        name << "target.dump." << call_idx << '.' << b;
+        std::ofstream f(name.str().c_str(), std::ios::out | std::ios::trunc);
+        const uint32_t len = (uint32_t)lens[b];
+        for (int64_t t = 0; t < T && !(t > 0 && (uint64_t)t >= len); t++) {
+            const float* row = o + (t * B + b) * F;
+            for (int64_t e = 0; e < F; e++) {
+                if (row[e] <= pruning) f << t << ' ' << e << ' ' << row[e] << '\n';
+            }
+        }
+    }
 }
 
 }  // namespace
@@ -68,13 +130,30 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
     TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == am_scores.size(1),
                 "start_end_states must have shape (2, B) with B = am_scores.size(1)");
     c10::cuda::CUDAGuard guard(am_scores.device());
-    (void)debug_options;  // text dumps (fbw_op.cu:155-224) are not produced
     // the outputs do not depend on the plan: allocate them while the plan is still being built
     torch::Tensor out  = torch::empty_like(am_scores);
     torch::Tensor sums = torch::empty({am_scores.size(0), am_scores.size(1)}, am_scores.options());
     Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, am_scores.size(0),
                               am_scores.size(2), (int64_t)num_states);
-    return run_impl(p, am_scores, false, out, sums);
+    // dumps every `dump_every`-th call of the process, counted like the reference's static batch_idx
+    // (fbw_op.cu:246, 390)
+    static std::atomic<unsigned> call_counter{0};
+    const unsigned call_idx = call_counter.fetch_add(1);
+    const bool dump_now = debug_options.dump_every > 0 && call_idx % debug_options.dump_every == 0;
+    torch::Tensor work;
+    auto result = run_impl(p, am_scores, false, out, sums, &work);
+    if (dump_now && debug_options.dump_alignment) {
+        auto stream = at::cuda::getCurrentCUDAStream();
+        torch::Tensor alpha = torch::empty({p.summary.T, p.summary.S}, am_scores.options());
+        check_status(fbw_b200_export_alpha(p.plan.data_ptr(), &p.summary, work.data_ptr(),
+                                           (size_t)work.numel(), alpha.data_ptr<float>(),
+                                           reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+        write_alignment_dump(alpha, start_end_states, seq_lens, debug_options.pruning, call_idx);
+    }
+    if (dump_now && debug_options.dump_output) {
+        write_output_dump(out, seq_lens, debug_options.pruning, call_idx);
+    }
+    return result;
 }
 
 // The op with the wrapper's passes folded in: log_probs (B,T,F) as the caller holds them ->

@@ -154,6 +154,15 @@ int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const
                         float* out, float* sums, float* loss2, void* work, size_t work_bytes,
                         fbw_b200_stream_t stream, float* phase_ms);
 
+/* Debug export for the text dumps of the reference (write_alignment_to_file, fbw_op.cu:155-195, which
+ * reads the per-frame forward state buffer kept at fbw_op.cu:304-315, 327-331): copies the forward
+ * state scores alpha_t(s) that the LAST fbw_b200_run / fbw_b200_run_fused left in `work` into `alpha`,
+ * a dense (T, S) f32 array indexed by frame and GLOBAL state id.  +inf for unreachable states, for
+ * state ids no sequence uses and for frames t >= seq_len; row 0 of a sequence without valid frames is
+ * its initial vector (0 at the start state).  Enqueues on `stream`; `work` must not have been reused. */
+int fbw_b200_export_alpha(const void* plan, const fbw_b200_summary* summary, const void* work,
+                          size_t work_bytes, float* alpha, fbw_b200_stream_t stream);
+
 /* Number of kernels of this library launched by this process so far (its own kernels only, not
  * the CUB sort/scan kernels it calls during prepare).  No counterpart in the reference. */
 int64_t fbw_b200_launch_count(void);
