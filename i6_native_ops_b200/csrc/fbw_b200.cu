@@ -2143,3 +2143,4 @@ extern "C" int fbw_b200_export_alpha(const void* plan, const fbw_b200_summary* s
 }
 
 #include "viterbi_b200.inc"
+#include "topology_b200.inc"

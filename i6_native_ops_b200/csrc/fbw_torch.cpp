@@ -248,7 +248,69 @@ py::tuple fbw_run_phases(const PlanHandle& h, torch::Tensor& am_scores) {
     return py::make_tuple(outs, times);
 }
 
+// Device-side automaton builders (no counterpart in the reference).  Both return the `fsa` tuple of
+// fbw_loss / align_viterbi: (num_states, edges (4,E) int32, weights (E,) float32, start_end (2,B) int32).
+py::tuple ctc_topology(torch::Tensor& labels, torch::Tensor& label_lens, int64_t blank) {
+    check_input(labels, torch::kInt32, "labels");
+    check_input(label_lens, torch::kInt32, "label_lens");
+    TORCH_CHECK(labels.dim() == 2 && labels.size(0) > 0 && labels.size(1) > 0, "labels must have shape (B, Lmax)");
+    TORCH_CHECK(label_lens.dim() == 1 && label_lens.size(0) == labels.size(0), "label_lens must have shape (B,)");
+    c10::cuda::CUDAGuard guard(labels.device());
+    auto stream = reinterpret_cast<fbw_b200_stream_t>(at::cuda::getCurrentCUDAStream().stream());
+    const int64_t B = labels.size(0), Lmax = labels.size(1);
+    size_t sbytes = fbw_b200_topology_bytes(B);
+    torch::Tensor scratch = byte_buffer(sbytes, labels.device());
+    int64_t S = 0, E = 0;
+    check_status(fbw_b200_ctc_topology_count(labels.data_ptr<int32_t>(), label_lens.data_ptr<int32_t>(), B,
+                                             Lmax, (int32_t)blank, scratch.data_ptr(), sbytes, &S, &E, stream));
+    torch::Tensor edges     = torch::empty({4, E}, labels.options());
+    torch::Tensor weights   = torch::empty({E}, labels.options().dtype(torch::kFloat32));
+    torch::Tensor start_end = torch::empty({2, B}, labels.options());
+    check_status(fbw_b200_ctc_topology_fill(labels.data_ptr<int32_t>(), label_lens.data_ptr<int32_t>(), B,
+                                            Lmax, (int32_t)blank, scratch.data_ptr(), E,
+                                            edges.data_ptr<int32_t>(), weights.data_ptr<float>(),
+                                            start_end.data_ptr<int32_t>(), stream));
+    return py::make_tuple(S, edges, weights, start_end);
+}
+
+py::tuple hmm_topology(torch::Tensor& classes, torch::Tensor& lens, c10::optional<torch::Tensor> optional,
+                       double loop_weight, double forward_weight, c10::optional<double> skip_weight) {
+    check_input(classes, torch::kInt32, "classes");
+    check_input(lens, torch::kInt32, "lens");
+    TORCH_CHECK(classes.dim() == 2 && classes.size(0) > 0 && classes.size(1) > 0, "classes must have shape (B, Nmax)");
+    TORCH_CHECK(lens.dim() == 1 && lens.size(0) == classes.size(0), "lens must have shape (B,)");
+    const uint8_t* opt = nullptr;
+    if (optional.has_value()) {
+        check_input(*optional, torch::kUInt8, "optional");
+        TORCH_CHECK(optional->sizes() == classes.sizes(), "optional must have the shape of classes");
+        opt = optional->data_ptr<uint8_t>();
+    }
+    c10::cuda::CUDAGuard guard(classes.device());
+    auto stream = reinterpret_cast<fbw_b200_stream_t>(at::cuda::getCurrentCUDAStream().stream());
+    const int64_t B = classes.size(0), Nmax = classes.size(1);
+    const int skip_all = skip_weight.has_value() ? 1 : 0;
+    size_t sbytes = fbw_b200_topology_bytes(B);
+    torch::Tensor scratch = byte_buffer(sbytes, classes.device());
+    int64_t S = 0, E = 0;
+    check_status(fbw_b200_hmm_topology_count(lens.data_ptr<int32_t>(), opt, B, Nmax, skip_all,
+                                             scratch.data_ptr(), sbytes, &S, &E, stream));
+    TORCH_CHECK(E > 0, "hmm_topology: no sequence has a state");
+    torch::Tensor edges     = torch::empty({4, E}, classes.options());
+    torch::Tensor weights   = torch::empty({E}, classes.options().dtype(torch::kFloat32));
+    torch::Tensor start_end = torch::empty({2, B}, classes.options());
+    check_status(fbw_b200_hmm_topology_fill(classes.data_ptr<int32_t>(), lens.data_ptr<int32_t>(), opt, B, Nmax,
+                                            (float)loop_weight, (float)forward_weight,
+                                            (float)skip_weight.value_or(0.0), skip_all, scratch.data_ptr(),
+                                            E, edges.data_ptr<int32_t>(), weights.data_ptr<float>(),
+                                            start_end.data_ptr<int32_t>(), stream));
+    return py::make_tuple(S, edges, weights, start_end);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("ctc_topology", &ctc_topology, "CTC automata of a batch of label sequences, built on the device");
+    m.def("hmm_topology", &hmm_topology, "Left-to-right HMM automata of a batch of class sequences",
+          py::arg("classes"), py::arg("lens"), py::arg("optional") = py::none(), py::arg("loop_weight"),
+          py::arg("forward_weight"), py::arg("skip_weight") = py::none());
     m.def("fbw_run_phases", &fbw_run_phases, "fbw_run with per-kernel device times");
     m.def("launch_count", []() { return fbw_b200_launch_count(); });
     m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");

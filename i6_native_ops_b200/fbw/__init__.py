@@ -105,4 +105,72 @@ def fbw_loss_fused(log_probs, fsa, seq_lens):
     return FusedFastBaumWelchLoss.apply(log_probs.contiguous(), fsa, seq_lens)
 
 
-__all__ = ["core", "FastBaumWelchLoss", "fbw_loss", "FusedFastBaumWelchLoss", "fbw_loss_fused"]
+class PlanCache:
+    """Keeps the prepared (validated, sorted) form of automaton batches so that a batch that comes
+    back -- the same tensors in a later epoch, or several score tensors for one batch -- skips the
+    preparation kernels and their host synchronisation.  No counterpart in the reference, which
+    re-reads the unsorted edge list every frame.
+
+    A plan is keyed on the identity of the four automaton tensors and ``seq_lens`` (storage
+    address, shape and in-place version counter) plus ``num_states`` and the (T, F) of the scores;
+    the cache holds references to the key tensors, so an address cannot be reused while its entry
+    lives.  Tensors modified in place get a new version and therefore a new plan.  Least recently
+    used entries are dropped beyond ``capacity``."""
+
+    def __init__(self, capacity: int = 8):
+        self.capacity = int(capacity)
+        self._entries = {}  # key -> (plan handle, key tensors); dicts keep insertion order
+        self.hits = 0
+        self.misses = 0
+
+    @staticmethod
+    def _key(fsa, seq_lens, T, F):
+        num_states, edges, weights, start_end = fsa
+        ident = tuple((t.data_ptr(), tuple(t.shape), t._version, str(t.device))
+                      for t in (edges, weights, start_end, seq_lens))
+        return (int(num_states), int(T), int(F)) + ident
+
+    def plan(self, fsa, seq_lens, T: int, F: int):
+        """The plan handle for ``core.fbw_run`` (built on a miss)."""
+        key = self._key(fsa, seq_lens, T, F)
+        hit = self._entries.pop(key, None)
+        if hit is None:
+            self.misses += 1
+            num_states, edges, weights, start_end = fsa
+            hit = (core.fbw_prepare(edges, weights, start_end, seq_lens, int(T), int(F), int(num_states)),
+                   (edges, weights, start_end, seq_lens))
+        else:
+            self.hits += 1
+        self._entries[key] = hit  # most recently used last
+        while len(self._entries) > self.capacity:
+            self._entries.pop(next(iter(self._entries)))
+        return hit[0]
+
+    def clear(self):
+        self._entries.clear()
+
+
+class CachedFastBaumWelchLoss(torch.autograd.Function):
+    """:class:`FastBaumWelchLoss` with the automaton preparation taken from a :class:`PlanCache`."""
+
+    @staticmethod
+    def forward(ctx, am_scores, fsa, seq_lens, cache):
+        handle = cache.plan(fsa, seq_lens, am_scores.shape[0], am_scores.shape[2])
+        grad, loss, _ = core.fbw_run(handle, am_scores)
+        ctx.save_for_backward(grad)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        return ctx.saved_tensors[0].neg().exp(), None, None, None
+
+
+def fbw_loss_cached(log_probs, fsa, seq_lens, cache: PlanCache):
+    """Same result and gradient as :func:`fbw_loss`; automata already seen by ``cache`` are not
+    prepared again."""
+    neg_log_probs = log_probs.neg().transpose(0, 1).contiguous()  # (T, B, F)
+    return CachedFastBaumWelchLoss.apply(neg_log_probs, fsa, seq_lens, cache)
+
+
+__all__ = ["core", "FastBaumWelchLoss", "fbw_loss", "FusedFastBaumWelchLoss", "fbw_loss_fused",
+           "PlanCache", "CachedFastBaumWelchLoss", "fbw_loss_cached"]

@@ -163,6 +163,39 @@ int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const
 int fbw_b200_export_alpha(const void* plan, const fbw_b200_summary* summary, const void* work,
                           size_t work_bytes, float* alpha, fbw_b200_stream_t stream);
 
+/* Device-side builders of the automaton tensors (edges (4,E) i32, weights (E) f32, start_end (2,B)
+ * i32, num_states) from label sequences.  No counterpart in the reference, whose automata come from an
+ * external exporter (only the tuple format is defined, i6_native_ops/fbw/__init__.py:49-63).
+ * Two steps, because the edge count depends on the labels:
+ *   *_count  writes per-sequence offsets into `scratch` (fbw_b200_topology_bytes(B) bytes, 256-byte
+ *            aligned) and returns the totals in HOST variables (SYNCHRONISES the stream);
+ *   *_fill   writes the tensors the caller allocated with those totals (enqueue only).
+ * State ids are global and consecutive per sequence.
+ * CTC: labels (B,Lmax) i32, label_lens (B) i32.  Local states 0..2L alternate blank/label plus one
+ *   separate final state 2L+1; an edge emits its target's symbol; loop, advance, and skip between
+ *   different labels; each edge entering one of the last two states has a copy entering the final
+ *   state; weights 0; start = first state, end = final state.
+ * HMM chain: classes (B,Nmax) i32, lens (B) i32, optional (B,Nmax) u8 or NULL.  Virtual start state 0,
+ *   state i+1 carries classes[i]; edge 0->1 weight 0; per state a loop (loop_weight), a forward edge
+ *   (forward_weight) and a j->j+2 edge: everywhere with skip_weight if skip_all != 0, else with
+ *   forward_weight around the states whose `optional` flag is set.  Weights are negative log values. */
+size_t fbw_b200_topology_bytes(int64_t B);
+int fbw_b200_ctc_topology_count(const int32_t* labels, const int32_t* label_lens, int64_t B,
+                                int64_t Lmax, int32_t blank, void* scratch, size_t scratch_bytes,
+                                int64_t* num_states, int64_t* num_edges, fbw_b200_stream_t stream);
+int fbw_b200_ctc_topology_fill(const int32_t* labels, const int32_t* label_lens, int64_t B,
+                               int64_t Lmax, int32_t blank, const void* scratch, int64_t num_edges,
+                               int32_t* edges, float* weights, int32_t* start_end,
+                               fbw_b200_stream_t stream);
+int fbw_b200_hmm_topology_count(const int32_t* lens, const uint8_t* optional, int64_t B, int64_t Nmax,
+                                int skip_all, void* scratch, size_t scratch_bytes,
+                                int64_t* num_states, int64_t* num_edges, fbw_b200_stream_t stream);
+int fbw_b200_hmm_topology_fill(const int32_t* classes, const int32_t* lens, const uint8_t* optional,
+                               int64_t B, int64_t Nmax, float loop_weight, float forward_weight,
+                               float skip_weight, int skip_all, const void* scratch,
+                               int64_t num_edges, int32_t* edges, float* weights, int32_t* start_end,
+                               fbw_b200_stream_t stream);
+
 /* Number of kernels of this library launched by this process so far (its own kernels only, not
  * the CUB sort/scan kernels it calls during prepare).  No counterpart in the reference. */
 int64_t fbw_b200_launch_count(void);
