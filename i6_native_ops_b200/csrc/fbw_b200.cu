@@ -1178,13 +1178,14 @@ __global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
                         cur = r[j].y;
                         mn  = y;
                         sme = 1.f;
-                    } else if (y < CUDART_INF_F) {
-                        if (y < mn) {
-                            sme = sme * __expf(y - mn) + 1.f;  // exp(-inf) = 0 if mn was +inf
-                            mn  = y;
-                        } else {
-                            sme += __expf(mn - y);
-                        }
+                    } else {
+                        // running (minimum, sum scaled to it) without branches: the frames of a warp
+                        // disagree on which term is the smaller, and both sides of a branch would run
+                        const float nm = fminf(mn, y);
+                        const float t1 = nm < CUDART_INF_F ? __expf(nm - mn) : 0.f;  // exp(-inf) = 0 while mn = +inf
+                        const float t2 = y < CUDART_INF_F ? __expf(nm - y) : 0.f;
+                        sme = sme * t1 + t2;
+                        mn  = nm;
                     }
                 }
             }
