@@ -58,7 +58,7 @@ typedef long long i64;
 struct PlanLayout {
     size_t header;
     size_t state_key, skey, skey_out, siota, sorted_state, packed_of;            // [S]
-    size_t scount, ecount, state_off, edge_off, slot_off;                        // int[B+1]
+    size_t scount, ecount, unordered, state_off, edge_off, slot_off;             // int[B+1]; unordered: int[4]
     size_t seq_T, start_l, end_l, nslot;                                         // int[B]
     size_t ta_off, tg_off, gf_off, gu_off, pu_off;                               // i64[B+1]
     size_t order, cost;                                                          // int[B], i64[B]
@@ -116,6 +116,7 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.packed_of    = take(4 * nS);
     L.scount       = take(4 * (nB + 1));
     L.ecount       = take(4 * (nB + 1));
+    L.unordered    = take(16);  // cleared together with the two count arrays before it
     L.state_off    = take(4 * (nB + 1));
     L.edge_off     = take(4 * (nB + 1));
     L.slot_off     = take(4 * (nB + 1));
@@ -263,13 +264,23 @@ __device__ __forceinline__ void claim_state(int* state_key, int* scount, int s, 
     }
 }
 
+// start state of a plan in one launch: header and counters zero, no state owned yet
+__global__ void k_init(fbw_b200_summary* hdr, int* state_key, i64 S, int* counters, i64 ncounters) {
+    const i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < S) state_key[i] = -1;
+    if (i < ncounters) counters[i] = 0;
+    if (i < (i64)(sizeof(fbw_b200_summary) / sizeof(int64_t))) reinterpret_cast<int64_t*>(hdr)[i] = 0;
+}
+
 // one thread per edge, then one per sequence: range checks, edge counts, state ownership
 __global__ void k_mark(const int* __restrict__ edges, const int* __restrict__ start_end, i64 E,
                        i64 B, i64 S, i64 F, int* state_key, int* scount, int* ecount,
-                       fbw_b200_summary* hdr) {
+                       int* unordered, fbw_b200_summary* hdr) {
     i64 idx = (i64)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < E) {
         int fr = edges[idx], to = edges[E + idx], em = edges[2 * E + idx], sq = edges[3 * E + idx];
+        // edges usually arrive sequence after sequence; then grouping them by sequence is the identity
+        if (idx > 0 && sq < edges[3 * E + idx - 1]) unordered[0] = 1;
         unsigned long long err = 0;
         if (fr < 0 || fr >= S || to < 0 || to >= S) err |= FBW_B200_ERR_STATE_RANGE;
         if (em < 0 || em >= F) err |= FBW_B200_ERR_EMISSION_RANGE;
@@ -333,12 +344,65 @@ __global__ void __launch_bounds__(1024) k_off1(const int* __restrict__ scount,
 }
 
 __global__ void k_statekeys(const int* __restrict__ state_key, i64 S, int B, unsigned* skey,
-                            int* siota) {
+                            int* siota, int* unordered) {
     i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x;
     if (s < S) {
         int k    = state_key[s];
         skey[s]  = k < 0 ? (unsigned)B : (unsigned)k;
         siota[s] = (int)s;
+        // state ids usually run sequence after sequence (unused ids last); then ordering the states
+        // by owning sequence is the identity
+        if (s > 0) {
+            const int kp = state_key[s - 1];
+            if ((k < 0 ? B : k) < (kp < 0 ? B : kp)) unordered[1] = 1;
+        }
+    }
+}
+
+// Stable grouping of n items by key (a counting sort with known group offsets `off`), one CTA:
+// perm[position] = item, inv[item] = position (inv may be null).  If the keys are already in
+// non-decreasing order (*unordered == 0) the grouping is the identity and is written as such; that
+// is the common case, and it replaces a device-wide radix sort (three kernels and two memsets) by
+// one short kernel.  Otherwise the items are taken 1024 at a time, the warps of a chunk one after
+// another, so that equal keys keep their order.
+constexpr int kGroupKeys = 8192;
+__global__ void __launch_bounds__(1024) k_group(const unsigned* __restrict__ keys, i64 n, int nkeys,
+                                                const int* __restrict__ off,
+                                                const int* __restrict__ unordered, int* perm, int* inv,
+                                                const fbw_b200_summary* hdr) {
+    __shared__ int cnt[kGroupKeys + 1];
+    if (hdr->error) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (*unordered == 0) {
+        for (i64 i = tid; i < n; i += 1024) {
+            perm[i] = (int)i;
+            if (inv) inv[i] = (int)i;
+        }
+        return;
+    }
+    for (int k = tid; k < nkeys; k += 1024) cnt[k] = 0;
+    __syncthreads();
+    for (i64 base = 0; base < n; base += 1024) {
+        const i64  i  = base + tid;
+        const bool in = i < n;
+        const unsigned k = in ? keys[i] : 0xffffffffu;  // items past the end form a group of their own
+        const unsigned peers = __match_any_sync(0xffffffffu, k);
+        const int rank   = __popc(peers & ((1u << lane) - 1u));
+        const int leader = __ffs(peers) - 1;
+        int first = 0;
+        for (int w = 0; w < 32; w++) {
+            if (warp == w && in && lane == leader) {
+                first = cnt[k];
+                cnt[k] = first + __popc(peers);
+            }
+            __syncthreads();
+        }
+        first = __shfl_sync(0xffffffffu, first, leader);
+        if (in) {
+            const int pos = off[k] + first + rank;
+            perm[pos] = (int)i;
+            if (inv) inv[i] = pos;
+        }
     }
 }
 
@@ -1616,9 +1680,13 @@ static int prepare_impl(const int32_t* edges, const float* weights, const int32_
     const bool fast = allow_fast && E > 0 && E / B <= kFastCap / 2 && F <= (i64)(1u << (32 - kFastPosBits));
 
     fbw_b200_summary* hdr = at<fbw_b200_summary>(plan, L.header);
-    CUDA_OK(cudaMemsetAsync(hdr, 0, sizeof(fbw_b200_summary), st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.state_key), 0xff, 4 * (size_t)S, st));
-    CUDA_OK(cudaMemsetAsync(at<int>(plan, L.scount), 0, L.state_off - L.scount, st));  // scount, ecount
+    {   // header, state owners, and the counters scount / ecount / unordered (one contiguous range)
+        const i64 ncounters = (i64)((L.state_off - L.scount) / 4);
+        const i64 n = S > ncounters ? S : ncounters;
+        k_init<<<(unsigned)((n + 255) / 256 > 0 ? (n + 255) / 256 : 1), 256, 0, st>>>(
+            hdr, at<int>(plan, L.state_key), S, at<int>(plan, L.scount), ncounters);
+        COUNT_LAUNCH(1);
+    }
     if (!fast) {
         CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_f), 0, 4 * (size_t)(S + 1), st));
         CUDA_OK(cudaMemsetAsync(at<int>(plan, L.rowcnt_b), 0, 4 * (size_t)(S + 1), st));
@@ -1632,26 +1700,46 @@ static int prepare_impl(const int32_t* edges, const float* weights, const int32_
     size_t cbytes = L.cub_temp_bytes;
 
     COUNT_LAUNCH(fast ? 7 : (E > 0 ? 9 : 5));  // k_mark, k_off1, k_statekeys, k_packed, k_off2 + edge kernels
+    int* unordered = at<int>(plan, L.unordered);
+    // grouping by sequence with one CTA instead of a device-wide sort (see k_group)
+    const bool group1 = fast && B < kGroupKeys;
     k_mark<<<blocks(E + B), TB, 0, st>>>(edges, start_end, E, B, S, F, at<int>(plan, L.state_key),
-                                         at<int>(plan, L.scount), at<int>(plan, L.ecount), hdr);
+                                         at<int>(plan, L.scount), at<int>(plan, L.ecount), unordered,
+                                         hdr);
     k_off1<<<1, 1024, 0, st>>>(at<int>(plan, L.scount), at<int>(plan, L.ecount), seq_lens, (int)B,
                                T, at<int>(plan, L.state_off), at<int>(plan, L.edge_off),
                                at<int>(plan, L.seq_T));
     // states ordered by owning sequence (stable: ascending state id inside a sequence)
     k_statekeys<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.state_key), S, (int)B,
-                                          at<unsigned>(plan, L.skey), at<int>(plan, L.siota));
-    CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.skey),
-                                            at<unsigned>(plan, L.skey_out),
-                                            at<int>(plan, L.siota), at<int>(plan, L.sorted_state),
-                                            (int)S, 0, bits_for((unsigned long long)B), st));
-    k_packed<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.sorted_state), S, at<int>(plan, L.packed_of));
+                                          at<unsigned>(plan, L.skey), at<int>(plan, L.siota),
+                                          unordered);
+    if (group1) {
+        // keys 0..B (B = state id not used by any sequence), group offsets = state_off[0..B]
+        k_group<<<1, 1024, 0, st>>>(at<unsigned>(plan, L.skey), S, (int)B + 1,
+                                    at<int>(plan, L.state_off), unordered + 1,
+                                    at<int>(plan, L.sorted_state), at<int>(plan, L.packed_of), hdr);
+    } else {
+        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.skey),
+                                                at<unsigned>(plan, L.skey_out),
+                                                at<int>(plan, L.siota), at<int>(plan, L.sorted_state),
+                                                (int)S, 0, bits_for((unsigned long long)B), st));
+        k_packed<<<blocks(S), TB, 0, st>>>(at<int>(plan, L.sorted_state), S, at<int>(plan, L.packed_of));
+    }
     if (fast) {
-        k_seqkeys<<<blocks(E), TB, 0, st>>>(edges, E, at<unsigned>(plan, L.keyq),
-                                            at<int>(plan, L.eiota), hdr);
-        CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyq),
-                                                at<unsigned>(plan, L.key32_out),
-                                                at<int>(plan, L.eiota), at<int>(plan, L.qe), (int)E,
-                                                0, bits_for((unsigned long long)B), st));
+        if (group1) {
+            // the sequence ids of the edges are the keys (validated by k_mark, which flags the plan
+            // otherwise), group offsets = edge_off
+            k_group<<<1, 1024, 0, st>>>(reinterpret_cast<const unsigned*>(edges + 3 * E), E, (int)B,
+                                        at<int>(plan, L.edge_off), unordered, at<int>(plan, L.qe),
+                                        nullptr, hdr);
+        } else {
+            k_seqkeys<<<blocks(E), TB, 0, st>>>(edges, E, at<unsigned>(plan, L.keyq),
+                                                at<int>(plan, L.eiota), hdr);
+            CUDA_OK(cub::DeviceRadixSort::SortPairs(ctemp, cbytes, at<unsigned>(plan, L.keyq),
+                                                    at<unsigned>(plan, L.key32_out),
+                                                    at<int>(plan, L.eiota), at<int>(plan, L.qe), (int)E,
+                                                    0, bits_for((unsigned long long)B), st));
+        }
         static bool attr_set[64] = {false};
         int dev = 0;
         CUDA_OK(cudaGetDevice(&dev));
