@@ -11,8 +11,10 @@ collective; one all-reduce of two loss scalars per step), i.e. weak scaling.
 
 Printed by rank 0: ONE JSON line.
   value      frames/s (T*B per call, summed over ranks) with inputs resident in HBM
-  e2e        the same through the op with HOST buffers: pinned host -> device copy of the scores
-             and automata, the op, device -> host copy of the (T,B) result, all inside the timing
+  e2e        the same through the op with HOST buffers: the scores stay in pinned host memory and the
+             op's gather reads the sectors it needs from there over the bus (--e2e-copy: the whole
+             tensor is copied to the device first), the automata are copied host -> device, the
+             (T,B) result device -> host, all inside the timing
   roofline   whole-call algorithmic bytes / measured call time against the measured HBM peak
   cpu_baseline  the CPU oracle (a C/OpenMP port of the reference's arithmetic; the reference has no
              CPU implementation of fbw) on a bounded sample of the same workload
@@ -289,15 +291,19 @@ def run_viterbi(args):
         am_h.copy_(am)
         host_fsa = [t.cpu().pin_memory() for t in (fsa[1], fsa[2], fsa[3], seq_lens)]
         align_h = torch.empty((batch.T, batch.B), dtype=torch.int32, pin_memory=True)
-        am_d = torch.empty_like(am)
         del am
-        h2d = am_h.numel() * 4 + sum(t.numel() * t.element_size() for t in host_fsa)
+        am_d = torch.empty(am_h.shape, dtype=am_h.dtype, device=dev) if args.e2e_copy else None
+        fsa_bytes = sum(t.numel() * t.element_size() for t in host_fsa)
+        h2d = (am_h.numel() * 4 if args.e2e_copy else batch.score_sector_bytes()) + fsa_bytes
         d2h = align_h.numel() * 4 + 4 * batch.B
 
         def e2e_step():
-            am_d.copy_(am_h, non_blocking=True)
             e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
-            alignment, scores = core.fast_viterbi(am_d, e_, w_, se_, sl_, S)
+            if args.e2e_copy:
+                am_d.copy_(am_h, non_blocking=True)
+                alignment, scores = core.fast_viterbi(am_d, e_, w_, se_, sl_, S)
+            else:  # the gather reads the scores it needs in place from pinned host memory
+                alignment, scores = core.fast_viterbi_host_scores(am_h, e_, w_, se_, sl_, S)
             align_h.copy_(alignment, non_blocking=True)
             return scores.cpu()  # device -> host read of the scores; synchronises
 
@@ -315,7 +321,10 @@ def run_viterbi(args):
             dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
         e2e = {"value": float(tot.item()) / (float(t_e.item()) * 1e-3), "unit": "frames/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": float(t_e.item()), "steps": n_e2e}
+               "ms_per_step": float(t_e.item()), "steps": n_e2e,
+               "path": ("scores copied to the device, then the op" if args.e2e_copy else
+                        "scores read in place from pinned host memory by the op's gather "
+                        f"(32-byte sectors; the whole tensor is {am_h.numel() * 4} bytes)")}
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -361,6 +370,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--op", default="fbw", choices=["fbw", "viterbi"])
+    ap.add_argument("--e2e-copy", action="store_true",
+                    help="e2e leg: copy the whole score tensor to the device first (default: the op reads "
+                         "the scores it needs from pinned host memory)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -483,15 +495,23 @@ def main():
         am_h.copy_(am)
         host_fsa = [t.cpu().pin_memory() for t in (fsa[1], fsa[2], fsa[3], seq_lens)]
         sums_h = torch.empty((batch.T, batch.B), dtype=torch.float32, pin_memory=True)
-        am_d = torch.empty_like(am)
         del am
-        h2d = am_h.numel() * 4 + sum(t.numel() * t.element_size() for t in host_fsa)
+        # The scores stay in pinned host memory: the op's gather reads the sectors it needs straight
+        # from there (no copy of the whole tensor), so what crosses the bus per step is those
+        # sectors plus the automata.  --e2e-copy takes the classic route instead (whole tensor copied
+        # to the device first).
+        am_d = torch.empty(am_h.shape, dtype=am_h.dtype, device=dev) if args.e2e_copy else None
+        fsa_bytes = sum(t.numel() * t.element_size() for t in host_fsa)
+        h2d = (am_h.numel() * 4 if args.e2e_copy else batch.score_sector_bytes()) + fsa_bytes
         d2h = sums_h.numel() * 4 + 8
 
         def e2e_step():
-            am_d.copy_(am_h, non_blocking=True)
             e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
-            out, sums, loss2, _ = sharding.sharded_fbw(am_d, (fsa[0], e_, w_, se_), sl_, plan=None)
+            if args.e2e_copy:
+                am_d.copy_(am_h, non_blocking=True)
+                out, sums, loss2, _ = sharding.sharded_fbw(am_d, (fsa[0], e_, w_, se_), sl_, plan=None)
+            else:
+                out, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_)
             sums_h.copy_(sums, non_blocking=True)
             return loss2.cpu()  # device -> host read of the reduced loss; synchronises
 
@@ -509,7 +529,10 @@ def main():
             dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
         e2e = {"value": total_frames / (float(t_e.item()) * 1e-3), "unit": "frames/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": float(t_e.item()), "steps": n_e2e}
+               "ms_per_step": float(t_e.item()), "steps": n_e2e,
+               "path": ("scores copied to the device, then the op" if args.e2e_copy else
+                        "scores read in place from pinned host memory by the op's gather "
+                        f"(32-byte sectors; the whole tensor is {am_h.numel() * 4} bytes)")}
 
     if rank == 0:
         peak, peak_kind = peaks()

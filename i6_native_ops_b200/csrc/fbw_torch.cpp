@@ -156,6 +156,41 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
     return result;
 }
 
+// The op on scores that live in PINNED HOST memory: am_scores (T,B,F) f32, a pinned CPU tensor, is
+// not copied to the device as a whole; the gather kernel reads the scores the automata need (one
+// 32-byte sector per distinct (frame, sequence, emission)) straight out of host memory through the
+// unified address space, which moves a fraction of the tensor over the bus.  Everything else, and the
+// results, are those of fbw().  No counterpart in the reference, which requires CUDA tensors
+// (fbw_torch.cpp:19-23).
+std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tensor& edges,
+                                           torch::Tensor& weights, torch::Tensor& start_end_states,
+                                           torch::Tensor& seq_lens, int64_t num_states) {
+    TORCH_CHECK(!am_scores.is_cuda() && am_scores.is_pinned(),
+                "am_scores must be a pinned host tensor (use fbw() for CUDA tensors)");
+    TORCH_CHECK(am_scores.is_contiguous() && am_scores.scalar_type() == torch::kFloat32,
+                "am_scores must be contiguous float32");
+    TORCH_CHECK(am_scores.dim() == 3, "am_scores must have shape (T, B, F)");
+    TORCH_CHECK(edges.is_cuda(), "edges must be a CUDA tensor");
+    TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == am_scores.size(1),
+                "start_end_states must have shape (2, B) with B = am_scores.size(1)");
+    c10::cuda::CUDAGuard guard(edges.device());
+    auto dev_opts = weights.options();  // float32 on the automata's device
+    torch::Tensor out  = torch::empty(am_scores.sizes(), dev_opts);
+    torch::Tensor sums = torch::empty({am_scores.size(0), am_scores.size(1)}, dev_opts);
+    Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, am_scores.size(0),
+                              am_scores.size(2), num_states);
+    auto   stream = at::cuda::getCurrentCUDAStream();
+    size_t wbytes = fbw_b200_run_bytes(&p.summary);
+    torch::Tensor work  = byte_buffer(wbytes, edges.device());
+    torch::Tensor loss2 = torch::empty({2}, dev_opts);
+    // pinned host memory is addressable from the device under unified addressing
+    check_status(fbw_b200_run(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
+                              out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
+                              work.data_ptr(), wbytes,
+                              reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    return {out, sums, loss2};
+}
+
 // The op with the wrapper's passes folded in: log_probs (B,T,F) as the caller holds them ->
 // [grad (B,T,F) = -posterior, sum_output (T,B)].  Replaces neg/transpose/contiguous before the op
 // and neg/exp after it (i6_native_ops/fbw/__init__.py:41-44, 66); opt-in, used by fbw_loss_fused.
@@ -315,6 +350,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("launch_count", []() { return fbw_b200_launch_count(); });
     m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");
     m.def("fbw_fused", &fbw_fused, "fbw on (B,T,F) log_probs, returning the gradient directly");
+    m.def("fbw_host_scores", &fbw_host_scores,
+          "fbw on scores in pinned host memory: only the scores the automata need cross the bus");
     m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
     m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
     m.def("abi_version", []() { return fbw_b200_abi_version(); });

@@ -23,21 +23,30 @@ std::vector<torch::Tensor> viterbi_impl(const torch::Tensor& scores_in, const to
                                         const torch::Tensor& weights,
                                         const torch::Tensor& start_end_states,
                                         const torch::Tensor& seq_lens, int64_t num_states,
-                                        bool batch_major) {
-    check_input(scores_in, torch::kFloat32, batch_major ? "log_probs" : "am_scores");
+                                        bool batch_major, bool host_scores = false) {
+    if (host_scores) {
+        TORCH_CHECK(!scores_in.is_cuda() && scores_in.is_pinned(),
+                    "scores must be a pinned host tensor (use fast_viterbi() for CUDA tensors)");
+        TORCH_CHECK(scores_in.is_contiguous() && scores_in.scalar_type() == torch::kFloat32,
+                    "scores must be contiguous float32");
+        TORCH_CHECK(edges.is_cuda(), "edges must be a CUDA tensor");
+    } else {
+        check_input(scores_in, torch::kFloat32, batch_major ? "log_probs" : "am_scores");
+    }
     TORCH_CHECK(scores_in.dim() == 3, "scores must have three dimensions");
     const int64_t B = scores_in.size(batch_major ? 0 : 1), T = scores_in.size(batch_major ? 1 : 0);
     const int64_t F = scores_in.size(2);
     TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == B,
                 "start_end_states must have shape (2, B) with B the batch size of the scores");
-    c10::cuda::CUDAGuard guard(scores_in.device());
-    auto int_opts = scores_in.options().dtype(torch::kInt32);
+    c10::cuda::CUDAGuard guard(edges.device());
+    auto int_opts = edges.options();      // int32 on the automata's device
+    auto f32_opts = weights.options();    // float32 on the automata's device
     torch::Tensor alignment = batch_major ? torch::empty({B, T}, int_opts) : torch::empty({T, B}, int_opts);
-    torch::Tensor scores    = torch::empty({B}, scores_in.options());
+    torch::Tensor scores    = torch::empty({B}, f32_opts);
     Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, T, F, num_states);
     auto   stream = at::cuda::getCurrentCUDAStream();
     size_t wbytes = fbw_b200_viterbi_bytes(&p.summary);
-    torch::Tensor work = byte_buffer(wbytes, scores_in.device());
+    torch::Tensor work = byte_buffer(wbytes, edges.device());
     check_status(fbw_b200_viterbi(p.plan.data_ptr(), &p.summary, scores_in.data_ptr<float>(),
                                   alignment.data_ptr<int32_t>(), scores.data_ptr<float>(),
                                   batch_major ? 1 : 0, work.data_ptr(), wbytes,
@@ -66,7 +75,20 @@ std::vector<torch::Tensor> fast_viterbi_batch_major(torch::Tensor& log_probs, to
     return viterbi_impl(log_probs, edges, weights, start_end_states, seq_lens, num_states, true);
 }
 
+// fast_viterbi on scores in PINNED HOST memory (a pinned CPU tensor, (T,B,F)): the gather kernel reads
+// the scores the automata need straight out of host memory through the unified address space instead
+// of the whole tensor being copied to the device first.  Same results.  No counterpart in the
+// reference, which requires CUDA tensors (binding.cpp:16-20).
+std::vector<torch::Tensor> fast_viterbi_host_scores(torch::Tensor& am_scores, torch::Tensor& edges,
+                                                    torch::Tensor& weights,
+                                                    torch::Tensor& start_end_states,
+                                                    torch::Tensor& seq_lens, int64_t num_states) {
+    return viterbi_impl(am_scores, edges, weights, start_end_states, seq_lens, num_states, false, true);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("fast_viterbi_host_scores", &fast_viterbi_host_scores,
+          "fast_viterbi on scores in pinned host memory: only the scores the automata need cross the bus");
     m.def("fast_viterbi", &fast_viterbi, "Fast Viterbi CUDA routine (B200)");
     m.def("fast_viterbi_batch_major", &fast_viterbi_batch_major,
           "fast_viterbi on (B,T,F) log_probs, returning the (B,T) alignment directly");

@@ -88,3 +88,15 @@ def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
     out, sums, loss2 = core.fbw_run(plan, am_scores)
     reduce_loss(loss2, group)
     return out, sums, loss2, plan
+
+
+def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None):
+    """:func:`sharded_fbw` for scores that live in pinned host memory: the op reads the scores it needs
+    in place (no copy of the whole tensor to the device).  Returns (out, sums, loss2_global)."""
+    from .fbw import core
+
+    num_states, edges, weights, start_end = fsa
+    out, sums, loss2 = core.fbw_host_scores(am_scores_pinned, edges, weights, start_end, seq_lens,
+                                            int(num_states))
+    reduce_loss(loss2, group)
+    return out, sums, loss2

@@ -60,10 +60,16 @@ class FbwBatch:
         B*F*4 bytes apart, so no two share a sector), the back-pointers of every valid frame written
         once and read once, and the (T,B) alignment plus the (B,) scores."""
         lens = self.seq_lens.astype(np.int64).clip(0, self.T)
+        ts = int((lens * self.states_per_seq).sum())
+        return self.score_sector_bytes() + 8 * ts + 4 * self.T * self.B + 4 * self.B
+
+    def score_sector_bytes(self) -> int:
+        """Bytes of the score tensor the ops actually read: one 32-byte sector per distinct
+        (valid frame, sequence, emission) triple."""
+        lens = self.seq_lens.astype(np.int64).clip(0, self.T)
         pairs = np.unique(self.edges[3].astype(np.int64) * self.F + self.edges[2].astype(np.int64))
         distinct = np.bincount(pairs // self.F, minlength=self.B)  # emissions per sequence
-        ts = int((lens * self.states_per_seq).sum())
-        return 32 * int((lens * distinct).sum()) + 8 * ts + 4 * self.T * self.B + 4 * self.B
+        return 32 * int((lens * distinct).sum())
 
 
 # ----------------------------------------------------------------------------------------------

@@ -4,7 +4,11 @@
  * reference's host launcher  fbw_cuda()  (i6_native_ops/fbw/fbw_op.cu:226-393), which its
  * binding  fbw()  (i6_native_ops/fbw/fbw_torch.cpp:15-29) calls with the same five arrays.
  *
- * All pointers are DEVICE pointers unless a comment says host.  Sizes are 64-bit.  No call
+ * All pointers are DEVICE pointers unless a comment says host.  Sizes are 64-bit.  The score tensor
+ * handed to fbw_b200_run / _run_fused / _viterbi may be ANY memory the device can address, in
+ * particular pinned host memory under unified addressing: the ops read it exactly once, and only the
+ * scores the automata refer to (one 32-byte sector per distinct frame/sequence/emission), so scores
+ * produced on the host need not be copied to the device as a whole.  No call
  * allocates device memory; scratch is passed in by the caller.  Calls enqueue work on the given
  * stream and return without synchronising, except fbw_b200_plan_summary.
  *

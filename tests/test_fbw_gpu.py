@@ -338,3 +338,22 @@ def test_fused_wrapper_matches_plain_wrapper(fbw_mod, cuda, name, kw):
     rows = -lp2.grad.sum(-1)
     valid = (torch.arange(b.T, device=cuda)[None, :] < sl[:, None])
     assert float((rows[valid] - 1).abs().max()) < 5e-3
+
+
+def test_scores_in_pinned_host_memory(fbw_mod, cuda):
+    """The op may read its scores in place from pinned host memory (the gather fetches the sectors it
+    needs over the bus): bit-identical to the run on a device copy, small case and pipelined case."""
+    for name, kw in [("monophone", dict()), ("triphone", dict(B=8, T=1500, F=12001))]:
+        b = wl.make_batch(name, **kw)
+        am = wl.make_scores(b, cuda)
+        fsa, sl = wl.to_torch(b, cuda)
+        am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
+        am_h.copy_(am)
+        out, sums = fbw_mod.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]), fbw_mod.core.DebugOptions())
+        out_h, sums_h, loss2 = fbw_mod.core.fbw_host_scores(am_h, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+        torch.cuda.synchronize()
+        assert out_h.is_cuda and torch.equal(sums_h, sums) and torch.equal(out_h, out)
+        assert abs(float(loss2[0]) - float(sums.double().sum())) <= 1e-4 * abs(float(sums.double().sum()))
+        del out, out_h, am
+    with pytest.raises(RuntimeError):  # pageable host memory is not addressable from the device
+        fbw_mod.core.fbw_host_scores(am_h.clone(), fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))

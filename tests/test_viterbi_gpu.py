@@ -240,3 +240,15 @@ def test_full_size_triphone(vit, ref_core, cuda):
                                         tied=False, name="triphone_full")
     report("viterbi:triphone_full", ms=ms, ref_op_ms=ref_ms, frames=int(am.shape[0] * am.shape[1]),
            vs_ref=vs_ref)
+
+
+def test_scores_in_pinned_host_memory(vit, cuda):
+    b = wl.make_batch("bpe_ctc", B=8, T=120, F=1025, scale=0.3)
+    fsa, sl = wl.to_torch(b, cuda)
+    am = -wl.make_scores(b, cuda)
+    am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
+    am_h.copy_(am)
+    a1, s1 = vit.core.fast_viterbi(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+    a2, s2 = vit.core.fast_viterbi_host_scores(am_h, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+    torch.cuda.synchronize()
+    assert a2.is_cuda and torch.equal(a1, a2) and torch.equal(s1, s2)
