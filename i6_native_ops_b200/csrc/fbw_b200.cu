@@ -1344,14 +1344,41 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
             }
             __syncwarp();
             int n;
-            do {  // patch the slots of this segment
-                const int d  = dlo + lane;
-                const int e  = d < Db ? emis[d] : 0x7fffffff;
-                const bool in = e < ce;
-                if (in) seg[e - cs] = pval(Pr[d]);
-                n = __popc(__ballot_sync(0xffffffffu, in));
-                dlo += n;
-            } while (n == 32);
+            if (Db * 8 > (int)F) {
+                // a row dense in classes (lattices): many slots fall into one segment, and a loop
+                // that loads 32 of them at a time is a chain of load latencies -- fetch four
+                // batches ahead (slots are in ascending emission id, so a batch that does not lie
+                // wholly in the segment ends the patching)
+                do {
+                    int   e[4];
+                    float pv[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int d = dlo + 32 * q + lane;
+                        e[q]  = d < Db ? emis[d] : 0x7fffffff;
+                        pv[q] = d < Db ? Pr[d] : 0.f;
+                    }
+                    n = 32;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (n == 32) {  // uniform: every earlier batch lay wholly in the segment
+                            const bool in = e[q] < ce;
+                            if (in) seg[e[q] - cs] = pval(pv[q]);
+                            n = __popc(__ballot_sync(0xffffffffu, in));
+                            dlo += n;
+                        }
+                    }
+                } while (n == 32);
+            } else {
+                do {  // patch the slots of this segment
+                    const int d  = dlo + lane;
+                    const int e  = d < Db ? emis[d] : 0x7fffffff;
+                    const bool in = e < ce;
+                    if (in) seg[e - cs] = pval(Pr[d]);
+                    n = __popc(__ballot_sync(0xffffffffu, in));
+                    dlo += n;
+                } while (n == 32);
+            }
             // make the generic-proxy writes visible to the async proxy, then one lane issues
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
