@@ -1538,7 +1538,8 @@ StreamPool* stream_pool() {
     return p;
 }
 
-// number of size groups (1 or 8): only batches whose largest automaton is several times the average
+// number of size groups (1 or 8): batches whose largest automaton is several times the average, and
+// large batches in general
 int choose_groups(const fbw_b200_summary& s) {
     static int forced = -1;
     if (forced < 0) {
@@ -1550,6 +1551,13 @@ int choose_groups(const fbw_b200_summary& s) {
         s.max_edges >= 2048) {
         return 8;
     }
+    // Large calls whose sweep CTAs (two per sequence) fill the machine also run as groups: every
+    // group's gather is an eighth of the whole, so the first sweeps start early, and the output
+    // stages of the groups that finish first overlap with the sweeps of the others.  (Measured on
+    // the triphone workload: B = 64 2.59 ms against 2.68 ms for the time-chunk pipeline, B = 128 4.53
+    // against 4.94; with B = 32 or 16 the time chunks win, 1.86 against 2.05 and 1.53 against 1.62.)
+    const double cells = (double)s.T * (double)s.B * (double)s.F;
+    if (cells >= 1.0e8 && 2 * s.B >= (i64)sm_count() * 4 / 5) return 8;
     return 1;
 }
 
@@ -1939,7 +1947,21 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     // ranges of the cost order, each launched with its own thread count and shared-memory size on
     // its own stream, so that small automata do not inherit the footprint of the largest one and
     // several of their CTAs share an SM.
-    const int G = ev ? 1 : choose_groups(s);
+    // Scores in host memory (read over the bus by the gather) make the gather the longest stage by
+    // far; the time-chunk pipeline, which keeps it running back to back, is then the better schedule
+    // (36.0 against 38.1 ms per call on the triphone workload).  Lattice-like batches keep their
+    // groups, which they need for their launch shapes.
+    bool host_scores = false;
+    {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, am) == cudaSuccess) {
+            host_scores = attr.type == cudaMemoryTypeHost;
+        } else {
+            (void)cudaGetLastError();  // an unregistered pointer is not an error here
+        }
+    }
+    int G = ev ? 1 : choose_groups(s);
+    if (G > 1 && host_scores && !(s.max_edges >= 2048 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E)) G = 1;
     const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     i64 ms = 0, me = 0, md = 0;
     for (int q = 0; q < FBW_B200_GROUPS; q++) {
@@ -1952,7 +1974,12 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         std::unique_lock<std::mutex> lock(pool->mu);
         CUDA_OK(cudaEventRecord(pool->fork, st));
         const int per = FBW_B200_GROUPS / G;  // base groups merged into one launch group
-        for (int g = 0; g < G; g++) {
+        // the cheapest group goes first: its sweeps end first and its output stages start while the
+        // expensive groups are still sweeping (FBW_B200_GROUP_ORDER=0: most expensive first)
+        static int reverse = -1;
+        if (reverse < 0) { const char* e = getenv("FBW_B200_GROUP_ORDER"); reverse = e ? atoi(e) : 1; }
+        for (int gi = 0; gi < G; gi++) {
+            const int g = reverse ? G - 1 - gi : gi;
             const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
             const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
             if (r1 <= r0) continue;
@@ -1962,13 +1989,13 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
                 ge_ = s.group_max_edges[q] > ge_ ? s.group_max_edges[q] : ge_;
                 gd_ = s.group_max_slots[q] > gd_ ? s.group_max_slots[q] : gd_;
             }
-            cudaStream_t gstream = g == 0 ? st : pool->aux[g];
-            if (g > 0) CUDA_OK(cudaStreamWaitEvent(gstream, pool->fork, 0));
+            cudaStream_t gstream = gi == 0 ? st : pool->aux[gi];
+            if (gi > 0) CUDA_OK(cudaStreamWaitEvent(gstream, pool->fork, 0));
             int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll);
             if (rc != FBW_B200_OK) return rc;
-            if (g > 0) {
-                CUDA_OK(cudaEventRecord(pool->join[g], gstream));
-                CUDA_OK(cudaStreamWaitEvent(st, pool->join[g], 0));
+            if (gi > 0) {
+                CUDA_OK(cudaEventRecord(pool->join[gi], gstream));
+                CUDA_OK(cudaStreamWaitEvent(st, pool->join[gi], 0));
             }
         }
     } else if (C > 1 && pool) {
