@@ -39,9 +39,10 @@ def _newer(target: str, sources) -> bool:
 
 def build_lib(force: bool = False, verbose: bool = False) -> str:
     src = os.path.join(PKG, "csrc", "fbw_b200.cu")
-    inc = os.path.join(PKG, "csrc", "viterbi_b200.inc")  # included by fbw_b200.cu
+    csrc = os.path.join(PKG, "csrc")
+    deps = [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cu", ".inc"))]  # the .inc files are included by fbw_b200.cu
     hdr = os.path.join(INCLUDE, "fbw_b200.h")
-    if not force and _newer(LIB, [src, inc, hdr]):
+    if not force and _newer(LIB, deps + [hdr]):
         return LIB
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
     cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB, src]
@@ -55,6 +56,7 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
 def _build_torch_ext(name: str, source: str, out_dir: str, target: str, force: bool, verbose: bool) -> str:
     src = os.path.join(PKG, "csrc", source)
     deps = [src, os.path.join(PKG, "csrc", "torch_common.h"), os.path.join(INCLUDE, "fbw_b200.h")]
+    build_lib(force, verbose)  # the extension links against the library: bring it up to date first
     if not force and _newer(target, deps):
         return target
     os.makedirs(out_dir, exist_ok=True)

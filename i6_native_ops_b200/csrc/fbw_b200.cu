@@ -69,7 +69,7 @@ struct PlanLayout {
     size_t head, hs, m_ptr;                                                      // int[E+1]
     size_t rowcnt_f, rowptr_f, rowcnt_b, rowptr_b;                               // int[S+1]
     size_t fwd_rec, bwd_rec;                                                     // uint2[E]
-    size_t q_rec, m_rec;                                                         // int4[E]
+    size_t q_rec;                                                                // int4[E]
     size_t slot_emis;                                                            // int[E]
     size_t cub_temp, cub_temp_bytes;
     size_t total;
@@ -156,7 +156,6 @@ PlanLayout plan_layout(i64 B, i64 E, i64 S) {
     L.fwd_rec      = take(8 * nE);
     L.bwd_rec      = take(8 * nE);
     L.q_rec        = take(16 * nE);
-    L.m_rec        = take(16 * nE);
     L.slot_emis    = take(4 * (nE + nB + 1));
     L.cub_temp_bytes = cub_temp_need(E, S);
     L.cub_temp       = take(L.cub_temp_bytes);
@@ -648,7 +647,7 @@ __global__ void __launch_bounds__(kFastThreads) k_seqsort(
     const int* __restrict__ edges, const float* __restrict__ weights, i64 E, i64 F,
     const int* __restrict__ qe, const int* __restrict__ edge_off, const int* __restrict__ state_off,
     const int* __restrict__ packed_of, int* rowptr_f, int* rowptr_b, uint2* fwd_rec, uint2* bwd_rec,
-    int4* q_rec, int4* m_rec, int2* m_pos, int* m_ptr, int* slot_emis, int* slot_off, int* nslot,
+    int4* q_rec, int2* m_pos, int* m_ptr, int* slot_emis, int* slot_off, int* nslot,
     fbw_b200_summary* hdr) {
     extern __shared__ __align__(16) unsigned char fast_raw[];
     FastSmem& sm = *reinterpret_cast<FastSmem*>(fast_raw);
@@ -710,8 +709,6 @@ __global__ void __launch_bounds__(kFastThreads) k_seqsort(
             const int i = (int)(keys[k] & pos_mask);
             sm.slot[i] = (unsigned short)slot;
             m_pos[e0 + j] = make_int2(i, slot);
-            m_rec[e0 + j] = make_int4((int)sm.from[i], (int)sm.to[i], slot,
-                                      __float_as_int(weights[qe[e0 + i]]));
         }
     }
     if (tid == 0) {
@@ -777,14 +774,14 @@ __global__ void __launch_bounds__(kFastThreads) k_seqsort(
     }
 }
 
-// the four sorted edge lists as records with sequence-local state ids and class slots
+// the sorted edge lists as records with sequence-local state ids and class slots
 __global__ void k_records(const int* __restrict__ edges, const float* __restrict__ weights, i64 E,
                           const int* __restrict__ packed_of, const int* __restrict__ state_off,
                           const int* __restrict__ slot_off, const int* __restrict__ slot_of_edge,
                           const int* __restrict__ qe, const int* __restrict__ fe,
                           const int* __restrict__ be, const int* __restrict__ me,
                           const int* __restrict__ qpos, const int* __restrict__ edge_off,
-                          uint2* fwd_rec, uint2* bwd_rec, int4* q_rec, int4* m_rec, int2* m_pos,
+                          uint2* fwd_rec, uint2* bwd_rec, int4* q_rec, int2* m_pos,
                           const fbw_b200_summary* hdr) {
     if (hdr->error) return;
     i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
@@ -805,7 +802,6 @@ __global__ void k_records(const int* __restrict__ edges, const float* __restrict
     rec(qe[i], fr, to, sl, w);
     q_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
     rec(me[i], fr, to, sl, w);
-    m_rec[i] = make_int4(fr, to, sl, __float_as_int(w));
     // (position in the sequence's ascending edge list, slot) for the class-posterior pass
     m_pos[i] = make_int2(qpos[me[i]] - edge_off[edges[3 * E + me[i]]], sl);
 }
@@ -819,13 +815,12 @@ struct RunArgs {
     float*       sums;
     float*       loss2;
     float *A, *Bt, *Gt, *Gf, *P, *X, *N;
-    int* status;  // device status word of the call (0 = ok)
     const int *state_off, *edge_off, *slot_off, *nslot, *seq_T, *start_l, *end_l;
     const i64 *ta_off, *tg_off, *gf_off, *gu_off, *pu_off, *tx_off;
     const int2* m_pos;
     const int *rowptr_f, *rowptr_b;
     const uint2 *fwd_rec, *bwd_rec;
-    const int4 *q_rec, *m_rec;
+    const int4* q_rec;
     const int *m_ptr, *slot_emis, *order;
     i64 T, B, F;
     int r0, r1;  // rank range (a group of sequences) this launch works on
@@ -1433,7 +1428,7 @@ __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i
 // host side
 // ---------------------------------------------------------------------------------------------
 struct RunLayout {
-    size_t status, A, Bt, Gt, Gf, P, X, N, carry, total;
+    size_t A, Bt, Gt, Gf, P, X, N, carry, total;
 };
 
 RunLayout run_layout(const fbw_b200_summary& s) {
@@ -1444,7 +1439,6 @@ RunLayout run_layout(const fbw_b200_summary& s) {
         off += ((floats + 8) * 4 + 255) & ~(size_t)255;  // slack: empty sequences read one float
         return o;
     };
-    L.status = take(56);
     L.A     = take((size_t)s.state_floats);
     L.Bt    = take((size_t)s.state_floats);
     L.Gt    = take((size_t)s.tiled_floats);
@@ -1457,16 +1451,97 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     return L;
 }
 
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-            n = 148;
-        }
+// the plan's arrays as kernel arguments: every sequence, one time chunk covering all frames
+void plan_args(RunArgs& a, const void* plan, const fbw_b200_summary& s) {
+    const PlanLayout L = plan_layout(s.B, s.E, s.S);
+    a.state_off = at<int>(plan, L.state_off);
+    a.edge_off  = at<int>(plan, L.edge_off);
+    a.slot_off  = at<int>(plan, L.slot_off);
+    a.nslot     = at<int>(plan, L.nslot);
+    a.seq_T     = at<int>(plan, L.seq_T);
+    a.start_l   = at<int>(plan, L.start_l);
+    a.end_l     = at<int>(plan, L.end_l);
+    a.ta_off = at<i64>(plan, L.ta_off);
+    a.tg_off = at<i64>(plan, L.tg_off);
+    a.gf_off = at<i64>(plan, L.gf_off);
+    a.gu_off = at<i64>(plan, L.gu_off);
+    a.pu_off = at<i64>(plan, L.pu_off);
+    a.tx_off = at<i64>(plan, L.tx_off);
+    a.m_pos  = at<int2>(plan, L.m_pos);
+    a.rowptr_f = at<int>(plan, L.rowptr_f);
+    a.rowptr_b = at<int>(plan, L.rowptr_b);
+    a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
+    a.bwd_rec  = at<uint2>(plan, L.bwd_rec);
+    a.q_rec    = at<int4>(plan, L.q_rec);
+    a.m_ptr     = at<int>(plan, L.m_ptr);
+    a.slot_emis = at<int>(plan, L.slot_emis);
+    a.order     = at<int>(plan, L.order);
+    a.T = s.T; a.B = s.B; a.F = s.F;
+    a.r0 = 0; a.r1 = (int)s.B;
+    a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
+}
+
+// the arguments of one forward-backward call: plan arrays, run scratch, inputs and outputs
+RunArgs fbw_args(const void* plan, const fbw_b200_summary& s, void* work, const RunLayout& R,
+                 const float* am, float* out, float* sums, float* loss2, int fused) {
+    RunArgs a;
+    memset(&a, 0, sizeof(a));
+    plan_args(a, plan, s);
+    a.am = am; a.out = out; a.sums = sums; a.loss2 = loss2;
+    a.A  = at<float>(work, R.A);
+    a.Bt = at<float>(work, R.Bt);
+    a.Gt = at<float>(work, R.Gt);
+    a.Gf = at<float>(work, R.Gf);
+    a.P  = at<float>(work, R.P);
+    a.X  = at<float>(work, R.X);
+    a.N  = at<float>(work, R.N);
+    a.carry = at<float>(work, R.carry);
+    a.fused = fused;
+    return a;
+}
+
+// largest per-group maxima of a plan: what a launch over all sequences has to be sized for
+void plan_maxima(const fbw_b200_summary& s, i64& ms, i64& me, i64& md) {
+    ms = me = md = 0;
+    for (int q = 0; q < FBW_B200_GROUPS; q++) {
+        ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
+        me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
+        md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
     }
-    return n;
+}
+
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
+}
+
+// SM count of the current device (asked once per device)
+int sm_count() {
+    static std::atomic<int> n[kMaxDevices];
+    const int dev = current_device();
+    int v = n[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+            v = 148;
+        }
+        n[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+// Raise a kernel's dynamic shared-memory limit to `smem` bytes unless an earlier launch on this
+// device already raised it that far (`granted` is the per-device record of one kernel).
+template <typename Kernel>
+cudaError_t grant_smem(Kernel kernel, std::atomic<int>* granted, size_t smem) {
+    if (smem <= 48 * 1024) return cudaSuccess;
+    const int dev = current_device();
+    if ((size_t)granted[dev].load(std::memory_order_relaxed) >= smem) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) granted[dev].store((int)smem, std::memory_order_relaxed);
+    return e;
 }
 
 std::atomic<long long> g_launches{0};
@@ -1482,10 +1557,8 @@ std::atomic<long long> g_launches{0};
 template <int RING, bool TILED, int KREG>
 int launch_sweep_k(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
                    int edges_in_smem, cudaStream_t st) {
-    if (smem > 48 * 1024) {
-        CUDA_OK(cudaFuncSetAttribute(k_sweep<RING, TILED, KREG>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
+    static std::atomic<int> granted[kMaxDevices];
+    CUDA_OK(grant_smem(k_sweep<RING, TILED, KREG>, granted, smem));
     k_sweep<RING, TILED, KREG><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
     COUNT_LAUNCH(1);
     return FBW_B200_OK;
@@ -1510,12 +1583,12 @@ struct StreamPool {
     cudaEvent_t  fork, join[FBW_B200_GROUPS];
     cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks];
 };
-StreamPool g_pools[64];
+StreamPool g_pools[kMaxDevices];
 std::mutex g_pools_mu;
 
 StreamPool* stream_pool() {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     StreamPool* p = &g_pools[dev];
     std::lock_guard<std::mutex> lk(g_pools_mu);
     if (p->failed) return nullptr;
@@ -1577,6 +1650,43 @@ int choose_chunks(const fbw_b200_summary& s) {
     return C;
 }
 
+// Launch shape of k_sweep for automata of at most ms states, me edges and md class slots.
+// Shared memory of the kernel: score ring, state rows (64 tiled or 2), row pointers, edge records.
+// Preference: edges in shared memory, then tiled state rows, then a deep score ring.
+struct SweepShape {
+    bool   found;
+    int    ring, tiled, in_smem, smax, dpmax, nt;
+    size_t smem;
+};
+SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
+    SweepShape c;
+    c.found = false;
+    c.ring = c.tiled = c.in_smem = 0;
+    c.smem  = 0;
+    c.smax  = (int)((ms + 3) & ~3);
+    c.dpmax = (int)((md + 3) & ~3);
+    c.nt    = (int)((ms + 31) & ~31);
+    c.nt    = c.nt < 64 ? 64 : (c.nt > 1024 ? 1024 : c.nt);
+    const size_t limit = 227 * 1024;
+    auto need = [&](int ring, int tiled, int in_smem) {
+        const size_t spad = tiled ? (size_t)(c.smax | 1) : (size_t)c.smax;
+        const size_t rows = tiled ? 64 : 2;
+        return (size_t)4 * ring * c.dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
+               (size_t)4 * ((c.smax + 2) & ~1) + (in_smem ? (size_t)8 * me : 0) + 16;
+    };
+    for (int es = 1; es >= 0 && !c.found; es--) {
+        for (int tl = 1; tl >= 0 && !c.found; tl--) {
+            for (int rg = 16; rg >= 0 && !c.found; rg = rg > 2 ? rg / 2 : rg - 2) {
+                if (need(rg, tl, es) <= limit) {
+                    c.ring = rg; c.tiled = tl; c.in_smem = es; c.found = true;
+                    c.smem = need(rg, tl, es);
+                }
+            }
+        }
+    }
+    return c;
+}
+
 // gather -> sweep -> posterior -> expand for the sequences of ranks [r0, r1) on stream st.
 // ms/me/md: largest state, edge and slot counts in the range (they size the sweep launch).
 enum { kDoGather = 1, kDoSweep = 2, kDoPost = 4, kDoExpand = 8, kDoAll = 15 };
@@ -1598,32 +1708,11 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
     if ((what & kDoSweep) && s.max_len > 0) {
-        int smax  = (int)((ms + 3) & ~3);
-        int dpmax = (int)((md + 3) & ~3);
-        int nt    = (int)((ms + 31) & ~31);
-        nt = nt < 64 ? 64 : (nt > 1024 ? 1024 : nt);
-        const size_t limit = 227 * 1024;
-        // shared memory of k_sweep: score ring, state rows (64 tiled or 2), row pointers, edges
-        auto need = [&](int ring, int tiled, int in_smem) {
-            const size_t spad = tiled ? (size_t)(smax | 1) : (size_t)smax;
-            const size_t rows = tiled ? 64 : 2;
-            return (size_t)4 * ring * dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
-                   (size_t)4 * ((smax + 2) & ~1) + (in_smem ? (size_t)8 * me : 0) + 16;
-        };
-        // preference: edges in shared memory, then tiled state rows, then a deep score ring
-        int ring = 0, tiled = 0, in_smem = 0;
-        bool found = false;
-        for (int es = 1; es >= 0 && !found; es--) {
-            for (int tl = 1; tl >= 0 && !found; tl--) {
-                for (int rg = 16; rg >= 0 && !found; rg = rg > 2 ? rg / 2 : rg - 2) {
-                    if (need(rg, tl, es) <= limit) {
-                        ring = rg; tiled = tl; in_smem = es; found = true;
-                    }
-                }
-            }
-        }
-        if (!found) return FBW_B200_TOO_LARGE;
-        const size_t smem = need(ring, tiled, in_smem);
+        const SweepShape c = sweep_shape(ms, me, md);
+        if (!c.found) return FBW_B200_TOO_LARGE;
+        const int smax = c.smax, dpmax = c.dpmax, nt = c.nt, ring = c.ring, tiled = c.tiled;
+        const int in_smem = c.in_smem;
+        const size_t smem = c.smem;
         const int grid = 2 * nb;
         int rc;
 #define SWEEP_CASE(R, TL) \
@@ -1775,19 +1864,13 @@ static int prepare_impl(const int32_t* edges, const float* weights, const int32_
                                                     at<int>(plan, L.eiota), at<int>(plan, L.qe), (int)E,
                                                     0, bits_for((unsigned long long)B), st));
         }
-        static bool attr_set[64] = {false};
-        int dev = 0;
-        CUDA_OK(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-            CUDA_OK(cudaFuncSetAttribute(k_seqsort, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)sizeof(FastSmem)));
-            if (dev >= 0 && dev < 64) attr_set[dev] = true;
-        }
+        static std::atomic<int> granted[kMaxDevices];
+        CUDA_OK(grant_smem(k_seqsort, granted, sizeof(FastSmem)));
         k_seqsort<<<(unsigned)B, kFastThreads, sizeof(FastSmem), st>>>(
             edges, weights, E, F, at<int>(plan, L.qe), at<int>(plan, L.edge_off),
             at<int>(plan, L.state_off), at<int>(plan, L.packed_of), at<int>(plan, L.rowptr_f),
             at<int>(plan, L.rowptr_b), at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec),
-            at<int4>(plan, L.q_rec), at<int4>(plan, L.m_rec), at<int2>(plan, L.m_pos),
+            at<int4>(plan, L.q_rec), at<int2>(plan, L.m_pos),
             at<int>(plan, L.m_ptr), at<int>(plan, L.slot_emis), at<int>(plan, L.slot_off),
             at<int>(plan, L.nslot), hdr);
     } else if (E > 0) {
@@ -1848,7 +1931,7 @@ static int prepare_impl(const int32_t* edges, const float* weights, const int32_
             at<int>(plan, L.slot_off), at<int>(plan, L.slot_of_edge), at<int>(plan, L.qe),
             at<int>(plan, L.fe), at<int>(plan, L.be), at<int>(plan, L.me), at<int>(plan, L.qpos),
             at<int>(plan, L.edge_off), at<uint2>(plan, L.fwd_rec), at<uint2>(plan, L.bwd_rec),
-            at<int4>(plan, L.q_rec), at<int4>(plan, L.m_rec), at<int2>(plan, L.m_pos), hdr);
+            at<int4>(plan, L.q_rec), at<int2>(plan, L.m_pos), hdr);
     }
     CUDA_OK(cudaGetLastError());
     return FBW_B200_OK;
@@ -1891,51 +1974,11 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     const fbw_b200_summary& s = *summary;
     const RunLayout  R = run_layout(s);
     if (work_bytes < R.total) return FBW_B200_WORKSPACE;
-    const PlanLayout L = plan_layout(s.B, s.E, s.S);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-
-    RunArgs a;
-    a.am = am; a.out = out; a.sums = sums; a.loss2 = loss2;
-    a.A  = at<float>(work, R.A);
-    a.Bt = at<float>(work, R.Bt);
-    a.Gt = at<float>(work, R.Gt);
-    a.Gf = at<float>(work, R.Gf);
-    a.P  = at<float>(work, R.P);
-    a.X  = at<float>(work, R.X);
-    a.N  = at<float>(work, R.N);
-    a.carry = at<float>(work, R.carry);
-    a.status = at<int>(work, R.status);
-    a.state_off = at<int>(plan, L.state_off);
-    a.edge_off  = at<int>(plan, L.edge_off);
-    a.slot_off  = at<int>(plan, L.slot_off);
-    a.nslot     = at<int>(plan, L.nslot);
-    a.seq_T     = at<int>(plan, L.seq_T);
-    a.start_l   = at<int>(plan, L.start_l);
-    a.end_l     = at<int>(plan, L.end_l);
-    a.ta_off = at<i64>(plan, L.ta_off);
-    a.tg_off = at<i64>(plan, L.tg_off);
-    a.gf_off = at<i64>(plan, L.gf_off);
-    a.gu_off = at<i64>(plan, L.gu_off);
-    a.pu_off = at<i64>(plan, L.pu_off);
-    a.tx_off = at<i64>(plan, L.tx_off);
-    a.m_pos  = at<int2>(plan, L.m_pos);
-    a.rowptr_f = at<int>(plan, L.rowptr_f);
-    a.rowptr_b = at<int>(plan, L.rowptr_b);
-    a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
-    a.bwd_rec  = at<uint2>(plan, L.bwd_rec);
-    a.q_rec    = at<int4>(plan, L.q_rec);
-    a.m_rec    = at<int4>(plan, L.m_rec);
-    a.m_ptr     = at<int>(plan, L.m_ptr);
-    a.slot_emis = at<int>(plan, L.slot_emis);
-    a.order     = at<int>(plan, L.order);
-    a.T = s.T; a.B = s.B; a.F = s.F;
-    a.r0 = 0; a.r1 = (int)s.B;
-    a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
-    a.fused = fused;
+    RunArgs a = fbw_args(plan, s, work, R, am, out, sums, loss2, fused);
 
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
-    CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
 
     // Large calls run as a pipeline over time chunks: both sweeps advance `chunk_steps` frames per
     // chunk from the two ends of every sequence.  The gather of the scores a chunk needs runs one
@@ -1963,13 +2006,17 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     int G = ev ? 1 : choose_groups(s);
     if (G > 1 && host_scores && !(s.max_edges >= 2048 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E)) G = 1;
     const int C = (ev || G > 1) ? 1 : choose_chunks(s);
-    i64 ms = 0, me = 0, md = 0;
-    for (int q = 0; q < FBW_B200_GROUPS; q++) {
-        ms = s.group_max_states[q] > ms ? s.group_max_states[q] : ms;
-        me = s.group_max_edges[q] > me ? s.group_max_edges[q] : me;
-        md = s.group_max_slots[q] > md ? s.group_max_slots[q] : md;
+    i64 ms, me, md;
+    plan_maxima(s, ms, me, md);
+    // every launch shape is checked before anything is enqueued, so that a call that cannot run
+    // fails before it has forked onto the auxiliary streams
+    if (s.max_len > 0) {
+        if (!sweep_shape(ms, me, md).found) return FBW_B200_TOO_LARGE;
     }
     StreamPool* pool = (C > 1 || G > 1) ? stream_pool() : nullptr;
+    // Once work has been forked onto auxiliary streams they are joined back into the caller's
+    // stream whatever happens: the caller may release the buffers in stream order after an error.
+    int rc_forked = FBW_B200_OK;
     if (G > 1 && pool) {
         std::unique_lock<std::mutex> lock(pool->mu);
         CUDA_OK(cudaEventRecord(pool->fork, st));
@@ -1990,12 +2037,18 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
                 gd_ = s.group_max_slots[q] > gd_ ? s.group_max_slots[q] : gd_;
             }
             cudaStream_t gstream = gi == 0 ? st : pool->aux[gi];
-            if (gi > 0) CUDA_OK(cudaStreamWaitEvent(gstream, pool->fork, 0));
+            if (gi > 0 && cudaStreamWaitEvent(gstream, pool->fork, 0) != cudaSuccess) {
+                rc_forked = FBW_B200_CUDA_ERROR;
+                break;
+            }
             int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll);
-            if (rc != FBW_B200_OK) return rc;
-            if (gi > 0) {
-                CUDA_OK(cudaEventRecord(pool->join[gi], gstream));
-                CUDA_OK(cudaStreamWaitEvent(st, pool->join[gi], 0));
+            if (gi > 0 && (cudaEventRecord(pool->join[gi], gstream) != cudaSuccess ||
+                           cudaStreamWaitEvent(st, pool->join[gi], 0) != cudaSuccess)) {
+                rc = rc != FBW_B200_OK ? rc : FBW_B200_CUDA_ERROR;
+            }
+            if (rc != FBW_B200_OK) {
+                rc_forked = rc;
+                break;
             }
         }
     } else if (C > 1 && pool) {
@@ -2009,47 +2062,51 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         const int first_finish = (int)((s.min_len / 2 - kTile > 0 ? s.min_len / 2 - kTile : 0) / J);
         cudaStream_t gs = pool->aux[0];
         CUDA_OK(cudaEventRecord(pool->fork, st));
-        CUDA_OK(cudaStreamWaitEvent(gs, pool->fork, 0));
-        for (int i = 1; i <= kPostStreams; i++) CUDA_OK(cudaStreamWaitEvent(pool->aux[i], pool->fork, 0));
+        auto ok = [&](cudaError_t e) {
+            if (e != cudaSuccess && rc_forked == FBW_B200_OK) rc_forked = FBW_B200_CUDA_ERROR;
+            return rc_forked == FBW_B200_OK;
+        };
+        auto stage = [&](int c, cudaStream_t on, int what) {
+            a.c_lo = c;
+            a.c_hi = c + 1;
+            const int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, on, nullptr, what);
+            if (rc != FBW_B200_OK && rc_forked == FBW_B200_OK) rc_forked = rc;
+            return rc_forked == FBW_B200_OK;
+        };
+        bool go = ok(cudaStreamWaitEvent(gs, pool->fork, 0));
+        for (int i = 1; i <= kPostStreams && go; i++) go = ok(cudaStreamWaitEvent(pool->aux[i], pool->fork, 0));
         // Enqueue stage by stage, not chunk by chunk: every gather first, then every sweep chunk,
         // then the output stages.  The streams are independent queues, so the GPU sees the same
         // dependencies, but the sweep chunks (the critical path) are all queued before the host
         // spends time on the many small launches of the output stages.
-        for (int c = 0; c < C && c <= last_gather; c++) {
-            a.c_lo = c;
-            a.c_hi = c + 1;
-            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, gs, nullptr, kDoGather);
-            if (rc != FBW_B200_OK) return rc;
-            CUDA_OK(cudaEventRecord(pool->gathered[c], gs));
+        for (int c = 0; c < C && c <= last_gather && go; c++) {
+            go = stage(c, gs, kDoGather) && ok(cudaEventRecord(pool->gathered[c], gs));
         }
-        for (int c = 0; c < C; c++) {
-            a.c_lo = c;
-            a.c_hi = c + 1;
-            if (c <= last_gather) CUDA_OK(cudaStreamWaitEvent(st, pool->gathered[c], 0));
-            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, nullptr, kDoSweep);
-            if (rc != FBW_B200_OK) return rc;
-            if (c == 0 || c >= first_finish) CUDA_OK(cudaEventRecord(pool->swept[c], st));
+        for (int c = 0; c < C && go; c++) {
+            if (c <= last_gather) go = ok(cudaStreamWaitEvent(st, pool->gathered[c], 0));
+            go = go && stage(c, st, kDoSweep);
+            if (go && (c == 0 || c >= first_finish)) go = ok(cudaEventRecord(pool->swept[c], st));
         }
         // the output stages of successive chunks go to different streams: each stage is a chain
         // of latency-bound kernels, several chunks' chains have to be in flight at once
-        for (int c = 0; c < C; c++) {
+        for (int c = 0; c < C && go; c++) {
             if (!(c == 0 || c >= first_finish)) continue;
-            a.c_lo = c;
-            a.c_hi = c + 1;
             cudaStream_t ps = pool->aux[1 + c % kPostStreams];
-            CUDA_OK(cudaStreamWaitEvent(ps, pool->swept[c], 0));
-            int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, ps, nullptr,
-                                  c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
-            if (rc != FBW_B200_OK) return rc;
+            go = ok(cudaStreamWaitEvent(ps, pool->swept[c], 0)) &&
+                 stage(c, ps, c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
         }
-        for (int i = 1; i <= kPostStreams; i++) {
-            CUDA_OK(cudaEventRecord(pool->join[i], pool->aux[i]));
-            CUDA_OK(cudaStreamWaitEvent(st, pool->join[i], 0));
+        // join: the gather stream and the output streams back into the caller's stream
+        for (int i = 0; i <= kPostStreams; i++) {
+            if (cudaEventRecord(pool->join[i], pool->aux[i]) != cudaSuccess ||
+                cudaStreamWaitEvent(st, pool->join[i], 0) != cudaSuccess) {
+                if (rc_forked == FBW_B200_OK) rc_forked = FBW_B200_CUDA_ERROR;
+            }
         }
     } else {
         int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kDoAll);
         if (rc != FBW_B200_OK) return rc;
     }
+    if (rc_forked != FBW_B200_OK) return rc_forked;
     if (ev) CUDA_OK(cudaEventRecord(ev[4], st));
     if (loss2) {
         k_loss<<<1, 1024, 0, st>>>(sums, s.T, s.B, loss2);
@@ -2112,13 +2169,13 @@ namespace {
 // address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with
 // that device current.
 std::mutex g_noalloc_mu;
-void*      g_noalloc_ptr[64]  = {nullptr};
-bool       g_noalloc_init[64] = {false};
+void*      g_noalloc_ptr[kMaxDevices]  = {nullptr};
+bool       g_noalloc_init[kMaxDevices] = {false};
 
 int noalloc_base(void** base) {
     int dev = 0;
     CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return FBW_B200_BAD_ARGUMENT;
+    if (dev < 0 || dev >= kMaxDevices) return FBW_B200_BAD_ARGUMENT;
     std::lock_guard<std::mutex> lk(g_noalloc_mu);
     if (!g_noalloc_init[dev]) {
         void* ptr = nullptr;
@@ -2141,15 +2198,16 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
     if (!am || !out || !sums) return FBW_B200_BAD_ARGUMENT;
     if (T <= 0 || B <= 0 || F <= 0 || S <= 0 || E < 0) return FBW_B200_BAD_ARGUMENT;
     if (((uintptr_t)out & 15) != 0) return FBW_B200_BAD_ARGUMENT;
-    // calls at or above this size take the multi-stream pipeline, which creates streams and events
+    // a fixed cap on the size of the score tensor: this entry runs every stage once, one after
+    // another on the caller's stream, which suits small and medium calls only
     if ((double)T * (double)B * (double)F >= 1.0e8) return FBW_B200_TOO_LARGE;
+    // the plan at the front of the array, the run scratch behind it; what can be told from the
+    // arguments alone is checked before anything runs
+    const size_t plan_bytes = (plan_layout(B, E, S).total + 255) & ~(size_t)255;
+    if (plan_bytes > kNoAllocBytes) return FBW_B200_TOO_LARGE;
     void* base = nullptr;
     int rc = noalloc_base(&base);  // first call on a device: looks the array's address up
     if (rc != FBW_B200_OK) return rc;
-
-    // the plan at the front of the array, the run scratch behind it
-    const size_t plan_bytes = (plan_layout(B, E, S).total + 255) & ~(size_t)255;
-    if (plan_bytes > kNoAllocBytes) return FBW_B200_TOO_LARGE;
     void* plan = base;
     rc = prepare_impl(edges, weights, start_end, seq_lens, T, B, F, E, S, plan, plan_bytes, stream, true);
     if (rc != FBW_B200_OK) return rc;
@@ -2162,61 +2220,20 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
         rc = fbw_b200_plan_summary(plan, &sum, stream);
     }
     if (rc != FBW_B200_OK) return rc;
+    // the size of the run scratch is known only now; the plan kernels have run on the array, the
+    // caller's outputs are untouched
     const RunLayout R = run_layout(sum);
     if (plan_bytes + R.total > kNoAllocBytes) return FBW_B200_TOO_LARGE;
     void* work = static_cast<unsigned char*>(base) + plan_bytes;
-    const PlanLayout L = plan_layout(sum.B, sum.E, sum.S);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-
-    RunArgs a;
-    a.am = am; a.out = out; a.sums = sums; a.loss2 = loss2;
-    a.A  = at<float>(work, R.A);
-    a.Bt = at<float>(work, R.Bt);
-    a.Gt = at<float>(work, R.Gt);
-    a.Gf = at<float>(work, R.Gf);
-    a.P  = at<float>(work, R.P);
-    a.X  = at<float>(work, R.X);
-    a.N  = at<float>(work, R.N);
-    a.carry  = at<float>(work, R.carry);
-    a.status = at<int>(work, R.status);
-    a.state_off = at<int>(plan, L.state_off);
-    a.edge_off  = at<int>(plan, L.edge_off);
-    a.slot_off  = at<int>(plan, L.slot_off);
-    a.nslot     = at<int>(plan, L.nslot);
-    a.seq_T     = at<int>(plan, L.seq_T);
-    a.start_l   = at<int>(plan, L.start_l);
-    a.end_l     = at<int>(plan, L.end_l);
-    a.ta_off = at<i64>(plan, L.ta_off);
-    a.tg_off = at<i64>(plan, L.tg_off);
-    a.gf_off = at<i64>(plan, L.gf_off);
-    a.gu_off = at<i64>(plan, L.gu_off);
-    a.pu_off = at<i64>(plan, L.pu_off);
-    a.tx_off = at<i64>(plan, L.tx_off);
-    a.m_pos  = at<int2>(plan, L.m_pos);
-    a.rowptr_f = at<int>(plan, L.rowptr_f);
-    a.rowptr_b = at<int>(plan, L.rowptr_b);
-    a.fwd_rec  = at<uint2>(plan, L.fwd_rec);
-    a.bwd_rec  = at<uint2>(plan, L.bwd_rec);
-    a.q_rec    = at<int4>(plan, L.q_rec);
-    a.m_rec    = at<int4>(plan, L.m_rec);
-    a.m_ptr     = at<int>(plan, L.m_ptr);
-    a.slot_emis = at<int>(plan, L.slot_emis);
-    a.order     = at<int>(plan, L.order);
-    a.T = sum.T; a.B = sum.B; a.F = sum.F;
-    a.r0 = 0; a.r1 = (int)sum.B;
-    a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
-    a.fused = 0;
+    RunArgs a = fbw_args(plan, sum, work, R, am, out, sums, loss2, 0);
 
     // The array keeps whatever the previous call left in it.  The plan builder clears its own
-    // counters; here the two things of the run that must start at zero are cleared.
+    // counters; of the run, only the sums must start at zero (the kernels write every other word
+    // they later read).
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(sum.T * sum.B), st));
-    CUDA_OK(cudaMemsetAsync(a.status, 0, sizeof(int), st));
-    i64 ms = 0, me = 0, md = 0;
-    for (int q = 0; q < FBW_B200_GROUPS; q++) {
-        ms = sum.group_max_states[q] > ms ? sum.group_max_states[q] : ms;
-        me = sum.group_max_edges[q] > me ? sum.group_max_edges[q] : me;
-        md = sum.group_max_slots[q] > md ? sum.group_max_slots[q] : md;
-    }
+    i64 ms, me, md;
+    plan_maxima(sum, ms, me, md);
     rc = launch_group(a, 0, (int)sum.B, ms, me, md, sum, st, nullptr, kDoAll);  // one stream, one chunk
     if (rc != FBW_B200_OK) return rc;
     if (loss2) {

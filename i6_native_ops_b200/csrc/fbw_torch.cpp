@@ -129,6 +129,8 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
     TORCH_CHECK(am_scores.dim() == 3, "am_scores must have shape (T, B, F)");
     TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == am_scores.size(1),
                 "start_end_states must have shape (2, B) with B = am_scores.size(1)");
+    check_input(edges, torch::kInt32, "edges");
+    check_same_device(am_scores, edges);
     c10::cuda::CUDAGuard guard(am_scores.device());
     // the outputs do not depend on the plan: allocate them while the plan is still being built
     torch::Tensor out  = torch::empty_like(am_scores);
@@ -201,6 +203,8 @@ std::vector<torch::Tensor> fbw_fused(torch::Tensor& log_probs, torch::Tensor& ed
     TORCH_CHECK(log_probs.dim() == 3, "log_probs must have shape (B, T, F)");
     TORCH_CHECK(start_end_states.dim() == 2 && start_end_states.size(1) == log_probs.size(0),
                 "start_end_states must have shape (2, B) with B = log_probs.size(0)");
+    check_input(edges, torch::kInt32, "edges");
+    check_same_device(log_probs, edges);
     c10::cuda::CUDAGuard guard(log_probs.device());
     const int64_t B = log_probs.size(0), T = log_probs.size(1), F = log_probs.size(2);
     torch::Tensor grad = torch::empty_like(log_probs);

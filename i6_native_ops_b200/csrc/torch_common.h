@@ -20,6 +20,12 @@ inline void check_input(const torch::Tensor& x, torch::ScalarType dtype, const c
     TORCH_CHECK(x.scalar_type() == dtype, name, " must have dtype ", dtype);
 }
 
+// device scores must live where the automata live
+inline void check_same_device(const torch::Tensor& scores, const torch::Tensor& edges) {
+    TORCH_CHECK(scores.device() == edges.device(),
+                "the scores and the automaton tensors must be on the same device");
+}
+
 inline void check_status(int status, const fbw_b200_summary* s = nullptr) {
     if (status == FBW_B200_OK) return;
     if (status == FBW_B200_BAD_AUTOMATON && s) {
@@ -57,6 +63,10 @@ inline Prepared prepare_impl(const torch::Tensor& edges, const torch::Tensor& we
     const int64_t B = start_end_states.size(1);
     TORCH_CHECK(seq_lens.dim() == 1 && seq_lens.size(0) == B, "seq_lens must have shape (B,)");
     TORCH_CHECK(T > 0 && B > 0 && F > 0, "am_scores must be non-empty");
+    // a kernel given another GPU's pointer faults (or, with peer access, silently reads remote memory)
+    TORCH_CHECK(weights.device() == edges.device() && start_end_states.device() == edges.device() &&
+                    seq_lens.device() == edges.device(),
+                "edges, weights, start_end_states and seq_lens must be on the same device");
     TORCH_CHECK(num_states > 0, "num_states must be positive");
 
     auto   stream = at::cuda::getCurrentCUDAStream();

@@ -32,6 +32,8 @@ std::vector<torch::Tensor> viterbi_impl(const torch::Tensor& scores_in, const to
         TORCH_CHECK(edges.is_cuda(), "edges must be a CUDA tensor");
     } else {
         check_input(scores_in, torch::kFloat32, batch_major ? "log_probs" : "am_scores");
+        check_input(edges, torch::kInt32, "edges");
+        check_same_device(scores_in, edges);
     }
     TORCH_CHECK(scores_in.dim() == 3, "scores must have three dimensions");
     const int64_t B = scores_in.size(batch_major ? 0 : 1), T = scores_in.size(batch_major ? 1 : 0);

@@ -48,7 +48,7 @@ def align_viterbi(
     :param log_probs: (B, T, F) float32 log probabilities of the emission model (CUDA)
     :param fsa: ``(num_states, edges (4,E) int32, weights (E,) float32, start_end_states (2,B) int32)``;
         edge rows are origin state, target state, emission index, sequence index
-    :param seq_lens: (B,) int32 number of valid frames per sequence
+    :param seq_lens: (B,) int32 number of valid frames per sequence, or a (T, B) index mask
     :param fold_transposes: read ``log_probs`` in place and write the (B, T) alignment directly
         (default); ``False`` takes the reference's route -- a (T, B, F) copy into ``core.fast_viterbi``
         and a transpose of its (T, B) result (``i6_native_ops/fast_viterbi/__init__.py:37-47``).
@@ -57,6 +57,10 @@ def align_viterbi(
         (B,) float32 best-path scores
     """
     num_states, edge_tensor, weight_tensor, start_end_states = fsa
+    if seq_lens.dim() == 2:  # (T, B) index mask: a length is the count of non-zero entries
+        if tuple(seq_lens.shape) != (log_probs.shape[1], log_probs.shape[0]):
+            raise RuntimeError("index mask must have shape (T, B)")
+        seq_lens = (seq_lens != 0).sum(0).to(torch.int32).contiguous()
     if fold_transposes:
         alignment, scores = core.fast_viterbi_batch_major(
             log_probs.contiguous(), edge_tensor, weight_tensor, start_end_states, seq_lens, int(num_states)

@@ -37,6 +37,17 @@ def _load_core():
 core = _load_core()
 
 
+def lengths_of(seq_lens: torch.Tensor, T: int, B: int) -> torch.Tensor:
+    """``seq_lens`` as the op wants it, (B,) int32.  Also accepts the older calling convention of a
+    (T, B) index mask (non-zero where a frame belongs to its sequence, valid frames first): a
+    sequence's length is then the number of non-zero entries of its column."""
+    if seq_lens.dim() == 2:
+        if tuple(seq_lens.shape) != (T, B):
+            raise RuntimeError(f"index mask must have shape (T, B) = ({T}, {B}), got {tuple(seq_lens.shape)}")
+        return (seq_lens != 0).sum(0).to(torch.int32).contiguous()
+    return seq_lens
+
+
 class FastBaumWelchLoss(torch.autograd.Function):
     """``FastBaumWelchLoss.apply(neg_log_probs (T,B,F), fsa, seq_lens) -> (T,B)`` per-frame sums.
 
@@ -47,6 +58,7 @@ class FastBaumWelchLoss(torch.autograd.Function):
     @staticmethod
     def forward(ctx, am_scores, fsa, seq_lens):
         num_states, edge_tensor, weight_tensor, start_end_states = fsa
+        seq_lens = lengths_of(seq_lens, am_scores.shape[0], am_scores.shape[1])
         grad, loss = core.fbw(
             am_scores, edge_tensor, weight_tensor, start_end_states, seq_lens, int(num_states),
             core.DebugOptions(),
@@ -70,7 +82,7 @@ def fbw_loss(
     :param log_probs: (B, T, F) float32 log probabilities (CUDA)
     :param fsa: ``(num_states, edges (4,E) int32 rows from/to/emission/sequence,
         weights (E,) float32, start_end_states (2,B) int32)``
-    :param seq_lens: (B,) int32 lengths
+    :param seq_lens: (B,) int32 lengths, or a (T, B) index mask (non-zero on the valid frames)
     :return: (T, B) per-frame normalisers (each valid frame of a sequence holds that sequence's
         negative log likelihood; frames past its length hold 0), as the reference returns
         (``i6_native_ops/fbw/__init__.py:66-68``).  ``loss.sum().backward()`` leaves
@@ -89,6 +101,7 @@ class FusedFastBaumWelchLoss(torch.autograd.Function):
     @staticmethod
     def forward(ctx, log_probs, fsa, seq_lens):
         num_states, edge_tensor, weight_tensor, start_end_states = fsa
+        seq_lens = lengths_of(seq_lens, log_probs.shape[1], log_probs.shape[0])
         grad, loss = core.fbw_fused(log_probs, edge_tensor, weight_tensor, start_end_states,
                                     seq_lens, int(num_states))
         ctx.save_for_backward(grad)
@@ -184,5 +197,5 @@ def fbw_loss_cached(log_probs, fsa, seq_lens, cache: PlanCache):
     return CachedFastBaumWelchLoss.apply(neg_log_probs, fsa, seq_lens, cache)
 
 
-__all__ = ["core", "FastBaumWelchLoss", "fbw_loss", "FusedFastBaumWelchLoss", "fbw_loss_fused",
+__all__ = ["core", "FastBaumWelchLoss", "fbw_loss", "lengths_of", "FusedFastBaumWelchLoss", "fbw_loss_fused",
            "PlanCache", "CachedFastBaumWelchLoss", "fbw_loss_cached", "fbw_host_scores"]

@@ -23,7 +23,8 @@ def sequence_costs(states_per_seq, edges_per_seq, seq_lens, T: int, F: int,
 
 def partition(costs: Sequence[float], world_size: int) -> List[np.ndarray]:
     """Longest-processing-time greedy partition.  Returns, per rank, the ascending indices of
-    its sequences.  Every rank gets at least one sequence when there are enough."""
+    its sequences.  Every rank gets at least one sequence when there are enough; with fewer
+    sequences than ranks some shards are empty (``sharded_fbw`` copes with that)."""
     costs = np.asarray(costs, dtype=np.float64)
     n = len(costs)
     if world_size < 1:
@@ -75,10 +76,26 @@ def reduce_loss(loss2, group=None):
     return loss2
 
 
+def _empty_step(am_scores, device):
+    """Results of a rank whose shard has no sequence (fewer sequences than ranks): nothing to run,
+    zero loss -- the rank still has to take part in the all-reduce or the others would wait for it."""
+    import torch
+
+    T = am_scores.shape[0]
+    out = torch.empty(tuple(am_scores.shape), dtype=torch.float32, device=device)
+    sums = torch.zeros((T, 0), dtype=torch.float32, device=device)
+    return out, sums, torch.zeros(2, dtype=torch.float32, device=device)
+
+
 def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
     """One data-parallel step on this rank's shard: run the op on the local sequences and
     all-reduce the loss scalars on the same stream.  Returns (out, sums, loss2_global, plan);
-    pass ``plan`` back in to reuse the prepared automata with new scores."""
+    pass ``plan`` back in to reuse the prepared automata with new scores.  A rank with an empty
+    shard (``am_scores.shape[1] == 0``) skips the op and contributes zeros to the reduction."""
+    if am_scores.shape[1] == 0:
+        out, sums, loss2 = _empty_step(am_scores, am_scores.device)
+        reduce_loss(loss2, group)
+        return out, sums, loss2, None
     from .fbw import core
 
     num_states, edges, weights, start_end = fsa
@@ -92,10 +109,15 @@ def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
 
 def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None):
     """:func:`sharded_fbw` for scores that live in pinned host memory: the op reads the scores it needs
-    in place (no copy of the whole tensor to the device).  Returns (out, sums, loss2_global)."""
+    in place (no copy of the whole tensor to the device).  Returns (out, sums, loss2_global).  An empty
+    shard is handled as in :func:`sharded_fbw`."""
+    num_states, edges, weights, start_end = fsa
+    if am_scores_pinned.shape[1] == 0:
+        out, sums, loss2 = _empty_step(am_scores_pinned, edges.device)
+        reduce_loss(loss2, group)
+        return out, sums, loss2
     from .fbw import core
 
-    num_states, edges, weights, start_end = fsa
     out, sums, loss2 = core.fbw_host_scores(am_scores_pinned, edges, weights, start_end, seq_lens,
                                             int(num_states))
     reduce_loss(loss2, group)

@@ -211,12 +211,14 @@ int64_t fbw_b200_launch_count(void);
  * 64 MiB, held by every GPU that loads the library until the process exits).  Same inputs and
  * outputs as fbw_b200_prepare + fbw_b200_run; loss2 may be NULL.  It has no counterpart in the
  * reference, whose launcher allocates and frees per call (fbw_op.cu:283-286, 384-389).
- *  - Returns FBW_B200_TOO_LARGE when plan + scratch exceed the capacity, or when T*B*F >= 1e8 (such
- *    calls run as a multi-stream pipeline, which creates streams); nothing has run then.
- *  - Calls no cudaMalloc/cudaFree and no allocating library routine.  SYNCHRONISES the stream once
- *    (the host reads the plan summary).
+ *  - Returns FBW_B200_TOO_LARGE when plan + scratch exceed the capacity, or when T*B*F >= 1e8 (a fixed
+ *    cap: this entry runs its stages one after another on the caller's stream, which suits small and
+ *    medium calls).  `out`, `sums` and `loss2` are untouched then; if only the run scratch did not fit,
+ *    the plan kernels have already run on the array and the stream has been synchronised.
+ *  - Calls no cudaMalloc/cudaFree and no allocating library routine.  SYNCHRONISES the stream on
+ *    every call (the host reads the plan summary), so it cannot be part of a stream capture.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, that
- *    device current); make that first call before any stream capture starts.
+ *    device current); make that first call before any stream capture starts on that device.
  *  - All calls on a device share the one array: two calls that overlap on the GPU (different
  *    streams or threads) race on it.  The array keeps the previous call's contents; everything a call
  *    needs to start from zero it clears itself. */

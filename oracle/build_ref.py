@@ -17,6 +17,11 @@ import os
 import sys
 
 
+def default_reference_root() -> str:
+    """Where the reference checkout lies: $I6_NATIVE_OPS_REFERENCE, else /root/reference."""
+    return os.environ.get("I6_NATIVE_OPS_REFERENCE", "/root/reference")
+
+
 def ref_dir() -> str:
     return os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
 
@@ -25,8 +30,9 @@ def built_path() -> str:
     return os.path.join(ref_dir(), "fbw_core_ref.so")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str:
+def build(reference_root: str = None, verbose: bool = False) -> str:
     """Compile the reference op; returns the path of the shared object."""
+    reference_root = reference_root or default_reference_root()
     src = os.path.join(reference_root, "i6_native_ops", "fbw")
     if not os.path.isfile(os.path.join(src, "fbw_op.cu")):
         raise FileNotFoundError(f"reference sources not found under {reference_root}")
@@ -48,8 +54,9 @@ def viterbi_built_path() -> str:
     return os.path.join(ref_dir(), "viterbi", "fast_viterbi_core_ref.so")
 
 
-def build_viterbi(reference_root: str = "/root/reference", verbose: bool = False) -> str:
+def build_viterbi(reference_root: str = None, verbose: bool = False) -> str:
     """Compile the reference fast_viterbi op; returns the path of the shared object."""
+    reference_root = reference_root or default_reference_root()
     src = os.path.join(reference_root, "i6_native_ops", "fast_viterbi")
     if not os.path.isfile(os.path.join(src, "core.cu")):
         raise FileNotFoundError(f"reference sources not found under {reference_root}")
@@ -92,6 +99,6 @@ def load_viterbi_ref():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else default_reference_root()
     print(build(root, verbose=True))
     print(build_viterbi(root, verbose=True))

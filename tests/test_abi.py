@@ -54,3 +54,17 @@ def test_python_surface_mirrors_reference():
     assert (d.dump_alignment, d.dump_output, d.dump_every, d.pruning) == (False, False, 40, 10.0)
     assert list(inspect.signature(m.fbw_loss).parameters) == ["log_probs", "fsa", "seq_lens"]
     assert issubclass(m.FastBaumWelchLoss, __import__("torch").autograd.Function)
+
+
+def test_reference_import_paths_resolve():
+    """The shim package serves the reference's import paths (no kernel is launched)."""
+    import i6_native_ops_b200.compat as compat
+
+    compat.install()
+    import i6_native_ops.fast_viterbi as v
+    import i6_native_ops.fbw as f
+    import i6_native_ops_b200.fast_viterbi as nv
+    import i6_native_ops_b200.fbw as nf
+
+    assert f.fbw_loss is nf.fbw_loss and f.FastBaumWelchLoss is nf.FastBaumWelchLoss and f.core is nf.core
+    assert v.align_viterbi is nv.align_viterbi and v.core is nv.core

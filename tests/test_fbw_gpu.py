@@ -5,13 +5,12 @@ when its build is present under oracle/_ref/, the committed golden fixtures, the
 reference's own test asserts (test/fbw.py:47-64) and size-independent properties at full size.
 
 Tolerances (from the task statement): |d loss| / loss <= 1e-5; max-abs posterior error <= 1e-4
-against the reference op.  Against the fp64 oracle the posterior tolerance is the fp32 rounding
-of the score magnitude (the reference's own distance from fp64), stated per case.
+against the reference op wherever the reference reproduces itself to 5e-5.  On every case the new
+op must also be no farther from the fp64 oracle than the reference op is (factor 1.05, whole case
+and per sequence); the bars live in tests/parity_util.py.
 """
 import glob
-import json
 import os
-import sys
 
 import numpy as np
 import pytest
@@ -19,13 +18,12 @@ import torch
 
 import oracle
 from i6_native_ops_b200 import workloads as wl
+from parity_util import (LOSS_RTOL, POST_ATOL, check_padding, full_parity, load_ref_fbw, loss_rel_diff,
+                         post_abs_diff, report, run_new, run_ref)
 
 pytestmark = pytest.mark.gpu
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
-LOSS_RTOL = 1e-5
-POST_ATOL = 1e-4
 
 
 @pytest.fixture(scope="module")
@@ -37,122 +35,26 @@ def fbw_mod(cuda):
 
 @pytest.fixture(scope="module")
 def ref_core(cuda):
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import build_ref
-
-    return build_ref.load_ref()
-
-
-def report(name, **kv):
-    d = os.path.join(ROOT, "gpurun_out")
-    try:
-        os.makedirs(d, exist_ok=True)
-        with open(os.path.join(d, "parity.jsonl"), "a") as f:
-            f.write(json.dumps(dict(case=name, **kv)) + "\n")
-    except OSError:
-        pass
-
-
-def run_new(m, am, batch_or_tuple, dev):
-    if isinstance(batch_or_tuple, wl.FbwBatch):
-        fsa, sl = wl.to_torch(batch_or_tuple, dev)
-    else:
-        fsa, sl = batch_or_tuple
-    out, sums = m.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]), m.core.DebugOptions())
-    return out, sums
-
-
-def run_ref(ref, am, batch, dev):
-    fsa, sl = wl.to_torch(batch, dev)
-    out, sums = ref.fbw(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]), ref.DebugOptions())
-    torch.cuda.synchronize()
-    return out, sums
-
-
-def post_abs_diff(out_a, out_b, chunk=64):
-    """max |exp(-a) - exp(-b)| over a (T,B,F) pair, chunked over T to bound memory."""
-    worst = 0.0
-    for t0 in range(0, out_a.shape[0], chunk):
-        a = torch.exp(-out_a[t0:t0 + chunk].double())
-        b = torch.exp(-out_b[t0:t0 + chunk].double())
-        worst = max(worst, float((a - b).abs().max()))
-    return worst
-
-
-def loss_rel_diff(s_a, s_b):
-    valid = s_b != 0
-    if not bool(valid.any()):
-        return 0.0
-    return float(((s_a - s_b).abs()[valid] / s_b.abs()[valid]).max())
-
-
-def check_padding(out, sums, seq_lens, T):
-    """sums == 0 and out == +inf at and past seq_len (fbw_op.cu:120-124, 366-370)."""
-    t = torch.arange(T, device=out.device)[:, None]
-    pad = t >= seq_lens.to(out.device)[None, :].clamp(min=0)
-    bad_len = (seq_lens < 1) | (seq_lens > T)
-    pad = pad | bad_len.to(out.device)[None, :]
-    assert bool((sums[pad] == 0).all())
-    assert bool(torch.isinf(out[pad]).all())
+    return load_ref_fbw()
 
 
 CASES = [
-    ("ctc_tiny", dict(), 1e-4),
-    ("ctc_tiny", dict(shuffle_edges=True), 1e-4),
-    ("monophone", dict(), 5e-3),
-    ("triphone", dict(B=4, T=300, F=2001, scale=0.2), 5e-3),
-    ("bpe_ctc", dict(B=8, T=120, F=1025, scale=0.3), 5e-3),
-    ("lattice", dict(B=6, F=257, T=400, scale=0.2), 5e-3),
-    ("lattice", dict(B=5, F=64, T=300, scale=0.15, shuffle_edges=True), 5e-3),
+    ("ctc_tiny", dict()),
+    ("ctc_tiny", dict(shuffle_edges=True)),
+    ("monophone", dict()),
+    ("triphone", dict(B=4, T=300, F=2001, scale=0.2)),
+    ("bpe_ctc", dict(B=8, T=120, F=1025, scale=0.3)),
+    ("lattice", dict(B=6, F=257, T=400, scale=0.2)),
+    ("lattice", dict(B=5, F=64, T=300, scale=0.15, shuffle_edges=True)),
 ]
 
 
-@pytest.mark.parametrize("name,kw,tol64", CASES)
-def test_parity_vs_oracle_and_reference(fbw_mod, ref_core, cuda, name, kw, tol64):
+@pytest.mark.parametrize("name,kw", CASES)
+def test_parity_vs_oracle_and_reference(fbw_mod, ref_core, cuda, name, kw):
+    """Every sequence of the case against the fp64 oracle, the whole case against the reference op."""
     b = wl.make_batch(name, **kw)
     am = wl.make_scores(b, cuda)
-    out, sums = run_new(fbw_mod, am, b, cuda)
-    torch.cuda.synchronize()
-    fsa, sl = wl.to_torch(b, cuda)
-    check_padding(out, sums, sl, b.T)
-    am_h = am.cpu().numpy()
-    o64, s64 = oracle.fbw_oracle(am_h, b.edges, b.weights, b.start_end, b.seq_lens, b.num_states, "f64")
-    o32, s32 = oracle.fbw_oracle(am_h, b.edges, b.weights, b.start_end, b.seq_lens, b.num_states, "f32")
-    out_h, sums_h = out.cpu().numpy(), sums.cpu().numpy()
-    assert np.array_equal(sums_h == 0, s64 == 0)
-    assert np.array_equal(np.isinf(out_h), np.isinf(o64))
-    valid = s64 != 0
-    loss64 = float((np.abs(sums_h - s64)[valid] / np.abs(s64[valid])).max()) if valid.any() else 0.0
-    post64 = float(np.abs(np.exp(-out_h.astype(np.float64)) - np.exp(-o64)).max())
-    post32 = float(np.abs(np.exp(-out_h.astype(np.float64)) - np.exp(-o32.astype(np.float64))).max())
-    rows = np.exp(-out_h.astype(np.float64)).sum(-1)
-    # fp32 scores of magnitude M carry rounding ~ M * 2^-23, which appears 1:1 (relative) in
-    # posteriors and row sums; the reference has the same property (its distance from fp64 is
-    # recorded below as ref_post_vs_f64)
-    ulp_tol = 32 * float(np.abs(s64).max()) * 2.0 ** -23
-    row_err = float(np.abs(rows[valid] - 1.0).max()) if valid.any() else 0.0
-    rec = dict(kw=str(kw), loss_vs_f64=loss64, post_vs_f64=post64, post_vs_f32_oracle=post32,
-               row_sum_err=row_err, score_max=float(np.abs(s64).max()))
-    if ref_core is not None:
-        r_out, r_sums = run_ref(ref_core, am, b, cuda)
-        r_out2, r_sums2 = run_ref(ref_core, am, b, cuda)
-        rec["loss_vs_ref"] = loss_rel_diff(sums, r_sums)
-        rec["post_vs_ref"] = post_abs_diff(out, r_out)
-        rec["ref_vs_ref_post"] = post_abs_diff(r_out, r_out2)
-        rec["ref_post_vs_f64"] = float(np.abs(np.exp(-r_out.cpu().numpy().astype(np.float64)) - np.exp(-o64)).max())
-        rec["bit_identical_sums"] = bool(torch.equal(sums, r_sums))
-    report(name, **rec)
-    assert np.all(rows[~valid] == 0)
-    assert row_err <= max(1e-4, ulp_tol)
-    assert loss64 <= LOSS_RTOL
-    assert post64 <= max(tol64, ulp_tol)
-    if ref_core is not None:
-        assert bool(torch.equal(sums == 0, r_sums == 0))
-        assert bool(torch.equal(torch.isinf(out), torch.isinf(r_out)))
-        assert rec["loss_vs_ref"] <= LOSS_RTOL
-        # 1e-4 wherever the reference reproduces itself to that level; where its own atomics make
-        # two runs of it differ by more, twice that measured spread is the bar
-        assert rec["post_vs_ref"] <= max(POST_ATOL, 2 * rec["ref_vs_ref_post"])
+    full_parity(f"{name} {kw}", fbw_mod, ref_core, b, am, cuda, sample=64)
 
 
 def test_reference_unit_test_semantics(fbw_mod, cuda):
@@ -288,32 +190,24 @@ def test_full_size_triphone_properties(fbw_mod, ref_core, cuda):
     out2, sums2, _ = fbw_mod.core.fbw_run(plan, am)
     assert bool(torch.equal(sums, sums2))
     assert bool(torch.equal(out, out2))
-    del out2
+    del out2, sums2
     rec = dict(row_sum_err=worst)
     if ref_core is not None:
-        r_out, r_sums = run_ref(ref_core, am, b, cuda)
-        rec["loss_vs_ref"] = loss_rel_diff(sums, r_sums)
-        rec["post_vs_ref"] = post_abs_diff(out, r_out)
-        rec["bit_identical_sums"] = bool(torch.equal(sums, r_sums))
-        del out
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        r_out2, _ = run_ref(ref_core, am, b, cuda)
-        e1.record()
-        torch.cuda.synchronize()
-        rec["ref_op_ms"] = e0.elapsed_time(e1)  # the reference's own GPU op on the same device
-        e0.record()
-        o3 = fbw_mod.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, fsa[0], fbw_mod.core.DebugOptions())
-        e1.record()
-        torch.cuda.synchronize()
-        rec["new_op_ms"] = e0.elapsed_time(e1)
-        del o3
-        rec["ref_vs_ref_post"] = post_abs_diff(r_out, r_out2)
-        report("triphone_full", **rec)
-        assert rec["loss_vs_ref"] <= LOSS_RTOL
-        assert rec["post_vs_ref"] <= max(POST_ATOL, 2 * rec["ref_vs_ref_post"])
-    else:
-        report("triphone_full", **rec)
+        # steady-state time of the reference op and of the new op on this device, for the record
+        def timed(fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return r, e0.elapsed_time(e1)
+
+        opts = fbw_mod.core.DebugOptions()
+        _, rec["ref_op_ms"] = timed(lambda: run_ref(ref_core, am, b, cuda))
+        _, rec["new_op_ms"] = timed(lambda: fbw_mod.core.fbw(am, fsa[1], fsa[2], fsa[3], sl, fsa[0], opts))
+    del out, sums
+    # whole batch against two runs of the reference, eight sequences of it against the fp64 oracle
+    full_parity("triphone_full", fbw_mod, ref_core, b, am, cuda, sample=8, extra=rec)
 
 
 @pytest.mark.parametrize("name,kw", [("ctc_tiny", dict()), ("monophone", dict(B=6, T=180, scale=0.3)),

@@ -112,6 +112,53 @@ def test_two_rank_loss_all_reduce_gloo():
         assert np.allclose(loss2, want, rtol=1e-12)
 
 
+def _rank_main_few_sequences(rank, world, port, q):
+    """More ranks than sequences: the ranks without a sequence go through sharded_fbw itself (it
+    must skip the op and still join the reduction); the others reduce their oracle numbers."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = wl.make_batch("ctc_tiny", B=2)
+        costs = sharding.sequence_costs(full.states_per_seq, full.edges_per_seq, full.seq_lens,
+                                        full.T, full.F)
+        mine = sharding.partition(costs, world)[rank]
+        if len(mine) == 0:
+            am = torch.empty((full.T, 0, full.F))
+            fsa = (1, torch.empty((4, 0), dtype=torch.int32), torch.empty(0), torch.empty((2, 0), dtype=torch.int32))
+            out, sums, loss2, _ = sharding.sharded_fbw(am, fsa, torch.empty(0, dtype=torch.int32))
+            assert out.shape == (full.T, 0, full.F) and sums.shape == (full.T, 0)
+        else:
+            shard = wl.make_batch("ctc_tiny", seq_ids=mine)
+            _, sums = oracle.fbw_oracle(wl.make_scores(shard).numpy(), shard.edges, shard.weights,
+                                        shard.start_end, shard.seq_lens, shard.num_states, "f64")
+            loss2 = torch.tensor([sums.sum(), sums[0].sum()], dtype=torch.float32)
+            sharding.reduce_loss(loss2)
+        q.put((rank, loss2.tolist(), [int(i) for i in mine]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_more_ranks_than_sequences_gloo():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_rank_main_few_sequences, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(len(r[2]) for r in res) == [0, 1, 1]
+    full = wl.make_batch("ctc_tiny", B=2)
+    _, sums = oracle.fbw_oracle(wl.make_scores(full).numpy(), full.edges, full.weights, full.start_end,
+                                full.seq_lens, full.num_states, "f64")
+    for _, loss2, _ in res:  # every rank, the idle one included, holds the global sums
+        assert np.allclose(loss2, [sums.sum(), sums[0].sum()], rtol=1e-5)
+
+
 def test_reduce_loss_is_a_noop_without_a_group():
     t = torch.tensor([1.0, 2.0])
     assert torch.equal(sharding.reduce_loss(t.clone()), t)

@@ -5,7 +5,6 @@ the CPU oracle, against the reference op itself when its build is present under 
 against the committed golden fixtures (outputs of the reference op on a B200).
 """
 import glob
-import json
 import os
 import sys
 
@@ -15,6 +14,7 @@ import torch
 
 import oracle
 from i6_native_ops_b200 import workloads as wl
+from parity_util import report
 
 pytestmark = pytest.mark.gpu
 
@@ -35,16 +35,6 @@ def ref_core(cuda):
     import build_ref
 
     return build_ref.load_viterbi_ref()
-
-
-def report(name, **kv):
-    d = os.path.join(ROOT, "gpurun_out")
-    try:
-        os.makedirs(d, exist_ok=True)
-        with open(os.path.join(d, "parity.jsonl"), "a") as f:
-            f.write(json.dumps(dict(case=name, **kv)) + "\n")
-    except OSError:
-        pass
 
 
 def tensors(c, dev):
@@ -119,6 +109,9 @@ CASES = [
     ("bpe_ctc", dict(B=8, T=120, F=1025, scale=0.3), 0.5),
     ("lattice", dict(B=6, F=257, T=400, scale=0.2), None),
     ("lattice", dict(B=5, F=64, T=300, scale=0.15, shuffle_edges=True), 1.0),
+    # full-scale lattice automata: more states than a CTA has threads, the general plan builder
+    ("lattice", dict(B=8), None),
+    ("lattice", dict(B=6, F=1000, shuffle_edges=True), 1.0),
 ]
 
 
@@ -200,7 +193,8 @@ def test_golden(vit, cuda, path):
 
 
 def test_full_size_triphone(vit, ref_core, cuda):
-    """The headline workload (B=64, T=1500, F=12001): bit-exact against the reference op, timed."""
+    """The headline workload (B=64, T=1500, F=12001): bit-exact against the CPU oracle, compared per
+    sequence with repeated runs of the reference op, timed."""
     b = wl.make_batch("triphone")
     fsa, sl = wl.to_torch(b, cuda)
     am = -wl.make_scores(b, cuda)
@@ -230,16 +224,20 @@ def test_full_size_triphone(vit, ref_core, cuda):
     slack = 1e-3 * scores.abs()
     assert bool((scores >= emitted + sl * w_lo - slack).all())
     assert bool((scores <= emitted + sl * w_hi + slack).all())
+    c = dict(am=am.cpu().numpy(), edges=b.edges, weights=b.weights, start_end=b.start_end,
+             seq_lens=b.seq_lens, num_states=b.num_states)
+    o_alignment, o_scores = oracle.viterbi_oracle(c["am"], c["edges"], c["weights"], c["start_end"],
+                                                  c["seq_lens"], c["num_states"])
+    assert np.array_equal(scores.cpu().numpy(), o_scores)
+    assert np.array_equal(alignment.cpu().numpy(), o_alignment)
     ref_ms, vs_ref = None, None
     if ref_core is not None:
         torch.cuda.set_device(0)
         _, ref_ms = timed(lambda: ref_core.fast_viterbi(am, fsa[1], fsa[2], fsa[3], sl, S), 2)
-        c = dict(am=am.cpu().numpy(), edges=b.edges, weights=b.weights, start_end=b.start_end,
-                 seq_lens=b.seq_lens, num_states=b.num_states)
         vs_ref = compare_with_reference(ref_core, c, cuda, alignment.cpu().numpy(), scores.cpu().numpy(),
                                         tied=False, name="triphone_full")
     report("viterbi:triphone_full", ms=ms, ref_op_ms=ref_ms, frames=int(am.shape[0] * am.shape[1]),
-           vs_ref=vs_ref)
+           vs_oracle="bit-exact", vs_ref=vs_ref)
 
 
 def test_scores_in_pinned_host_memory(vit, cuda):

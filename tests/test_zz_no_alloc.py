@@ -3,15 +3,19 @@ memory while they run (a server with a memory pool frozen at start-up, a plug-in
 input and output buffers from its host).  Its plan and scratch live in a fixed array inside the
 library.  The test calls it through the C ABI with ctypes, twice in a row on different inputs (the
 array keeps the first call's contents, so the second call shows that stale contents do no harm),
-and checks both results against the regular entry points on the same inputs.  The file name makes
-pytest collect it last."""
+and checks the results against the regular entry points on the same inputs and against the fp64 CPU
+oracle.  A third call carries one automaton too large for the per-sequence plan builder, so the
+entry's own rebuild of the plan with the general builder is exercised.  The file name makes pytest
+collect it last."""
 import ctypes
 import os
 
+import numpy as np
 import pytest
 import torch
 
 from i6_native_ops_b200 import workloads as wl
+from parity_util import merge_batches, truth_distances
 
 pytestmark = pytest.mark.gpu
 
@@ -47,14 +51,20 @@ def test_noalloc_entry_matches_regular_entry_twice(cuda):
     lib.fbw_b200_fbw_noalloc.restype = ctypes.c_int
     lib.fbw_b200_noalloc_capacity.restype = ctypes.c_size_t
     assert lib.fbw_b200_noalloc_capacity() == 64 << 20
-    cases = [wl.make_batch("monophone", B=8, T=200, scale=0.3), wl.make_batch("ctc_tiny")]
+    small = wl.make_batch("lattice", B=11, F=257, T=600, scale=0.1)
+    large = wl.make_batch("lattice", seq_ids=[1002], F=257, T=600, scale=1.0)  # about 8700 edges
+    small.T = large.T = 600
+    large.seq_lens[:] = 600
+    mixed = merge_batches(small, large)
+    assert mixed.edges_per_seq.max() > 4096 and mixed.num_edges / mixed.B <= 2048
+    cases = [wl.make_batch("monophone", B=8, T=200, scale=0.3), wl.make_batch("ctc_tiny"), mixed]
     # The first call on a device is the set-up call: the CUDA module with the fixed array gets
     # loaded and the array's address is looked up.  Device memory is compared around later calls.
     b0 = cases[1]
     fsa0, sl0 = wl.to_torch(b0, cuda)
     assert _noalloc(lib, wl.make_scores(b0, cuda), fsa0, sl0)[0] == 0
     torch.cuda.synchronize()
-    for b in cases:  # two calls in a row; each finds the previous call's data in the array
+    for b in cases:  # calls in a row; each finds the previous call's data in the array
         am = wl.make_scores(b, cuda)
         fsa, sl = wl.to_torch(b, cuda)
         bufs = _outputs(am)  # the caller's output buffers exist before the call
@@ -72,6 +82,10 @@ def test_noalloc_entry_matches_regular_entry_twice(cuda):
         assert float(((sums - ref_sums).abs()[valid] / ref_sums.abs()[valid]).max()) <= LOSS_RTOL
         assert float((torch.exp(-out.double()) - torch.exp(-ref_out.double())).abs().max()) <= POST_ATOL
         assert abs(float(loss2[0]) - float(ref_sums.double().sum())) <= 1e-5 * float(ref_sums.double().sum())
+        # and against the truth: per-frame sums to 1e-5, posteriors to the fp32 rounding of the scores
+        post, loss, pattern_ok = truth_distances(b, am, [out], [sums], np.arange(b.B))
+        assert pattern_ok and loss.max() <= LOSS_RTOL
+        assert post.max() <= 4 * max(POST_ATOL, 64 * float(sums.abs().max()) * 2.0 ** -23)
 
 
 def test_noalloc_entry_rejects_what_does_not_fit(cuda):
