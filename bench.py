@@ -11,11 +11,18 @@ collective; one all-reduce of two loss scalars per step), i.e. weak scaling.
 
 Printed by rank 0: ONE JSON line.
   value      frames/s (T*B per call, summed over ranks) with inputs resident in HBM
-  e2e        the same through the op with HOST buffers: the scores stay in pinned host memory and the
-             op's gather reads the sectors it needs from there over the bus (--e2e-copy: the whole
-             tensor is copied to the device first), the automata are copied host -> device, the
-             (T,B) result device -> host, all inside the timing
+  e2e        the same through the op with HOST buffers, inputs AND results in pinned host memory: the
+             op's gather reads the score sectors it needs in place over the bus, its output pass writes
+             the (T,B,F) result in place, the automata are copied host -> device and the (T,B) sums and
+             the loss device -> host, all inside the timing.  Beside it: e2e_copy (whole tensors copied
+             both ways around the op) and e2e_out_on_device (result left on the device); each leg lists
+             every rank's time and bus throughput
   roofline   whole-call algorithmic bytes / measured call time against the measured HBM peak
+  strong     strong scaling of the two configurations that are sharded over GPUs: a fixed global batch
+             (lattice B=512, bpe_ctc B=256) partitioned by sequence over the N ranks; step time is the
+             slowest rank's, every rank's time and the partition's cost imbalance are listed
+  reference_gpu_op  the reference's own CUDA op on the same tensors and GPU (N=1 only; never inside a
+             timed region of this library)
   cpu_baseline  the CPU oracle (a C/OpenMP port of the reference's arithmetic; the reference has no
              CPU implementation of fbw) on a bounded sample of the same workload
 
@@ -44,9 +51,9 @@ import numpy as np  # noqa: E402
 SEQS_PER_GPU = {"triphone": 64, "bpe_ctc": 256, "monophone": 32, "ctc_tiny": 4, "lattice": 64}
 CPU_SAMPLE_SEQS = None  # None: the full per-GPU batch of the workload
 
-# dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one triphone call divided by the
-# call's algorithmic bytes, from the ncu capture summarised in profiles/
-TRAFFIC_PER_ALGORITHMIC_BYTE = 0.89  # profiles/dram_traffic_triphone_b16.md (B=16 capture, scaled)
+# dram__bytes_read.sum + dram__bytes_write.sum over all kernels of ONE op call, from an ncu capture
+# of exactly that workload and per-GPU batch size; other sizes report no traffic figure.
+MEASURED_TRAFFIC = {}  # (workload, sequences per GPU) -> bytes per call
 
 
 def peaks():
@@ -130,13 +137,21 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(use)}
 
 
-def cpu_baseline_pass(workload: str, threads: int, passes: int, warm: int = 1):
-    """Times the CPU oracle (test infrastructure; the only use of oracle/ in this file) on a
-    bounded sample: one per-GPU batch of the workload at full T and F, a few passes."""
+def cpu_baseline_pass(workload: str, threads: int, passes: int, warm: int = 1, gpus: int = 1,
+                      per_gpu: int = None):
+    """Times the CPU oracle (test infrastructure) on a bounded sample: one per-GPU batch of the
+    workload at full T and F -- with several GPUs the shard rank 0 gets -- a few passes."""
     import oracle
+    from i6_native_ops_b200 import sharding
     from i6_native_ops_b200 import workloads as wl
 
-    batch = wl.make_batch(workload, B=CPU_SAMPLE_SEQS or SEQS_PER_GPU[workload])
+    per_gpu = per_gpu or CPU_SAMPLE_SEQS or SEQS_PER_GPU[workload]
+    if gpus > 1:
+        full = wl.make_batch(workload, B=per_gpu * gpus)
+        costs = sharding.sequence_costs(full.states_per_seq, full.edges_per_seq, full.seq_lens, full.T, full.F)
+        batch = wl.make_batch(workload, seq_ids=sharding.partition(costs, gpus)[0], T=full.T)
+    else:
+        batch = wl.make_batch(workload, B=per_gpu)
     am = wl.make_scores(batch, "cpu").numpy()
     times = []
     for i in range(warm + passes):
@@ -149,6 +164,7 @@ def cpu_baseline_pass(workload: str, threads: int, passes: int, warm: int = 1):
     frames = batch.T * batch.B
     sample = (f"{batch.B} sequences of {workload} at full T={batch.T}, F={batch.F}; fp32 CPU port of the "
               f"reference arithmetic, OpenMP over sequences, {passes} passes")
+    cpu_baseline_pass.last_batch = batch
     return frames, times, sample
 
 
@@ -159,7 +175,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    frames, times, sample = cpu_baseline_pass(args.workload, threads, args.steps, max(1, min(args.warmup, 2)))
+    frames, times, sample = cpu_baseline_pass(args.workload, threads, args.steps, max(1, min(args.warmup, 2)),
+                                              gpus=max(1, args.gpus), per_gpu=args.seqs_per_gpu)
     total = float(sum(times))
     value = frames * len(times) / total
     line = {
@@ -167,7 +184,8 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": sample},
+        "config": config_of(args.workload, cpu_baseline_pass.last_batch,
+                            (args.seqs_per_gpu or SEQS_PER_GPU[args.workload]) * max(1, args.gpus)),
         "cpu_baseline": {"value": value, "unit": "frames/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -359,6 +377,82 @@ def run_viterbi(args):
         dist.destroy_process_group()
 
 
+def gpu_numa_cpus(index: int):
+    """CPUs local to GPU `index` (its PCI device's local_cpulist in sysfs), or None if not exposed."""
+    try:
+        import torch
+
+        pr = torch.cuda.get_device_properties(index)
+        bus = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/local_cpulist") as f:
+            text = f.read().strip()
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        return node, sorted(cpus)
+    except Exception:
+        return None
+
+
+def config_of(workload, batch, global_b):
+    """The `config` object of a bench line; the reference arm prints the same keys and values."""
+    am_bytes = 4 * batch.T * batch.B * batch.F
+    return {"workload": workload, "T": int(batch.T), "B_per_gpu": int(batch.B), "B_global": int(global_b),
+            "F": int(batch.F), "edges_per_gpu": int(batch.num_edges), "states_per_gpu": int(batch.num_states),
+            "partition": "by sequence, length-balanced",
+            "l2": (f"inputs ({am_bytes / 1e9:.2f} GB of scores per call) exceed the 126 MB L2; no flush"
+                   if am_bytes > 2 * 126e6 else "an L2 flush (256 MB write) runs between timed steps"),
+            "step": "prepare + run per call (automata re-sorted every step)"}
+
+
+STRONG = {"lattice": 512, "bpe_ctc": 256}  # workload -> fixed global batch of the strong-scaling legs
+
+
+def strong_leg(name, global_b, world, rank, dev, steps, dist, torch, core, sharding, wl):
+    """Strong scaling: a FIXED global batch of `global_b` sequences of workload `name` is partitioned
+    by sequence over the ranks (length-balanced), every rank runs the op on its shard, and the step
+    time is the slowest rank's.  Returns the report of the leg (identical on every rank)."""
+    full = wl.make_batch(name, B=global_b)
+    costs = sharding.sequence_costs(full.states_per_seq, full.edges_per_seq, full.seq_lens, full.T, full.F)
+    parts = sharding.partition(costs, world)
+    loads = np.array([costs[p].sum() for p in parts])
+    batch = wl.take_sequences(full, parts[rank])
+    am = wl.make_scores(batch, dev)
+    fsa, seq_lens = wl.to_torch(batch, dev)
+    for _ in range(3):
+        sharding.sharded_fbw(am, fsa, seq_lens)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        sharding.sharded_fbw(am, fsa, seq_lens)   # prepare + run + the all-reduce of the loss scalars
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    mine = ev[0].elapsed_time(ev[steps]) / steps
+    t = torch.tensor([mine], device=dev, dtype=torch.float64)
+    all_ms = [torch.zeros_like(t) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(all_ms, t)
+    else:
+        all_ms = [t]
+    rank_ms = [float(x.item()) for x in all_ms]
+    ms = max(rank_ms)
+    alg = full.algorithmic_bytes()
+    peak, _ = peaks()
+    del am
+    torch.cuda.empty_cache()
+    return {"B_global": int(global_b), "B_per_rank": [int(len(p)) for p in parts], "T": int(full.T),
+            "F": int(full.F), "steps": steps, "ms_per_step": ms, "frames_per_s": full.T * global_b / (ms * 1e-3),
+            "rank_ms": rank_ms, "cost_imbalance": float(loads.max() / loads.mean()),
+            "roofline_frac_per_gpu": alg / world / (ms * 1e-3) / 1e9 / peak,
+            "scaling": "strong"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -369,10 +463,12 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling legs (lattice, bpe_ctc)")
+    ap.add_argument("--no-reference-gpu-op", action="store_true")
     ap.add_argument("--op", default="fbw", choices=["fbw", "viterbi"])
     ap.add_argument("--e2e-copy", action="store_true",
-                    help="e2e leg: copy the whole score tensor to the device first (default: the op reads "
-                         "the scores it needs from pinned host memory)")
+                    help="viterbi e2e leg: copy the whole score tensor to the device first (default: the op "
+                         "reads the scores it needs from pinned host memory)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -397,6 +493,17 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # host threads and pinned buffers of a rank on the CPUs next to its GPU, where sysfs tells which
+    numa = gpu_numa_cpus(local_rank)
+    bound = False
+    if numa is not None and numa[1]:
+        try:
+            allowed = sorted(set(numa[1]) & set(os.sched_getaffinity(0)))
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                bound = True
+        except OSError:
+            pass
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -448,6 +555,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def gather_ranks(x):
+        """One float per rank -> list over ranks (on every rank)."""
+        t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+        if world == 1:
+            return [float(x)]
+        got = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(got, t)
+        return [float(g.item()) for g in got]
+
     clk = ClockSampler(local_rank).start()
     for _ in range(args.warmup):
         step()
@@ -488,70 +604,133 @@ def main():
     prep_ms = pe0.elapsed_time(pe1) / reps
     del plan
 
+    # ---- the reference's own GPU op on the same device and inputs (the incumbent; reported, never
+    # ---- part of a timed region of this library; oracle/_ref is test infrastructure) ----
+    reference_gpu_op = None
+    if world == 1 and not args.no_reference_gpu_op:
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "oracle"))
+            import build_ref
+
+            ref = build_ref.load_ref()
+            if ref is None:
+                reference_gpu_op = {"skipped": "oracle/_ref/fbw_core_ref.so is not built on this machine"}
+            elif batch.T * batch.B * batch.F >= 2 ** 32 or batch.B > 1024:
+                reference_gpu_op = {"skipped": "the reference op's 32-bit sizes / one-block launches cannot take this batch"}
+            else:
+                times = []
+                for i in range(7):
+                    pe0.record()
+                    r = ref.fbw(am, fsa[1], fsa[2], fsa[3], seq_lens, int(fsa[0]), ref.DebugOptions())
+                    pe1.record()
+                    torch.cuda.synchronize()
+                    del r
+                    if i >= 2:
+                        times.append(pe0.elapsed_time(pe1))
+                med = float(np.median(times))
+                reference_gpu_op = {"ms_per_call": med, "frames_per_s": frames / (med * 1e-3), "calls": len(times),
+                                    "what": "median of the unmodified reference op (i6_native_ops/fbw, built "
+                                            "from its own sources for sm_100a) on the same tensors, same GPU"}
+        except Exception as e:  # a report line, not the product: never fail the bench over it
+            reference_gpu_op = {"skipped": f"{type(e).__name__}: {e}"[:200]}
+
     # ---- end to end through the op with host buffers ----
-    e2e = None
+    e2e = e2e_copy = e2e_dev_out = None
     if not args.no_e2e:
         am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
         am_h.copy_(am)
         host_fsa = [t.cpu().pin_memory() for t in (fsa[1], fsa[2], fsa[3], seq_lens)]
         sums_h = torch.empty((batch.T, batch.B), dtype=torch.float32, pin_memory=True)
+        out_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
         del am
-        # The scores stay in pinned host memory: the op's gather reads the sectors it needs straight
-        # from there (no copy of the whole tensor), so what crosses the bus per step is those
-        # sectors plus the automata.  --e2e-copy takes the classic route instead (whole tensor copied
-        # to the device first).
-        am_d = torch.empty(am_h.shape, dtype=am_h.dtype, device=dev) if args.e2e_copy else None
+        torch.cuda.empty_cache()
         fsa_bytes = sum(t.numel() * t.element_size() for t in host_fsa)
-        h2d = (am_h.numel() * 4 if args.e2e_copy else batch.score_sector_bytes()) + fsa_bytes
-        d2h = sums_h.numel() * 4 + 8
+        out_bytes = out_h.numel() * 4
+        small_d2h = sums_h.numel() * 4 + 8
 
-        def e2e_step():
-            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
-            if args.e2e_copy:
-                am_d.copy_(am_h, non_blocking=True)
-                out, sums, loss2, _ = sharding.sharded_fbw(am_d, (fsa[0], e_, w_, se_), sl_, plan=None)
-            else:
-                out, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_)
+        def finish(sums, loss2):
             sums_h.copy_(sums, non_blocking=True)
             return loss2.cpu()  # device -> host read of the reduced loss; synchronises
 
-        n_e2e = max(3, min(args.steps, 10))
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        ev0.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        ev1.record()
-        barrier()
-        t_e = torch.tensor([ev0.elapsed_time(ev1) / n_e2e], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-        e2e = {"value": total_frames / (float(t_e.item()) * 1e-3), "unit": "frames/s",
-               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": float(t_e.item()), "steps": n_e2e,
-               "path": ("scores copied to the device, then the op" if args.e2e_copy else
-                        "scores read in place from pinned host memory by the op's gather "
-                        f"(32-byte sectors; the whole tensor is {am_h.numel() * 4} bytes)")}
+        def step_in_place():
+            # scores read in place from pinned host memory by the gather, the (T,B,F) result written
+            # in place into pinned host memory by the output pass: no staging copy in either direction
+            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
+            _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_, out=out_h)
+            return finish(sums, loss2)
 
+        def step_copy():
+            # the classic route: whole score tensor host -> device, op, whole result device -> host
+            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
+            am_d = am_h.to(dev, non_blocking=True)
+            out, sums, loss2, _ = sharding.sharded_fbw(am_d, (fsa[0], e_, w_, se_), sl_, plan=None)
+            out_h.copy_(out, non_blocking=True)
+            return finish(sums, loss2)
+
+        def step_dev_out():
+            # scores read in place, the (T,B,F) result left on the device (a trainer that consumes it there)
+            e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
+            _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_)
+            return finish(sums, loss2)
+
+        def time_leg(fn, h2d, d2h, path):
+            n = max(3, min(args.steps, 6))
+            for _ in range(2):
+                fn()
+            barrier()
+            ev0.record()
+            for _ in range(n):
+                fn()
+            ev1.record()
+            barrier()
+            mine = ev0.elapsed_time(ev1) / n
+            rank_ms = gather_ranks(mine)
+            t = max(rank_ms)
+            return {"value": total_frames / (t * 1e-3), "unit": "frames/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "ms_per_step": t, "steps": n, "path": path,
+                    "rank_ms": rank_ms,
+                    "rank_bus_gbs": [(h2d + d2h) / (m * 1e-3) / 1e9 for m in rank_ms]}
+
+        sectors = batch.score_sector_bytes()
+        e2e = time_leg(step_in_place, sectors + fsa_bytes, out_bytes + small_d2h,
+                       "inputs and results in pinned host memory: scores read in place by the op's gather "
+                       f"(32-byte sectors of a {am_h.numel() * 4}-byte tensor), the (T,B,F) result written in "
+                       "place by its output pass, sums and loss copied back")
+        e2e_copy = time_leg(step_copy, am_h.numel() * 4 + fsa_bytes, out_bytes + small_d2h,
+                            "whole score tensor copied host -> device, the op, whole result copied device -> host")
+        e2e_dev_out = time_leg(step_dev_out, sectors + fsa_bytes, small_d2h,
+                               "scores read in place from pinned host memory, the (T,B,F) result LEFT ON THE "
+                               "DEVICE, sums and loss copied back")
+        del am_h, out_h
+    else:
+        del am
+    torch.cuda.empty_cache()
+
+    # ---- strong scaling on the configurations that are sharded over GPUs ----
+    strong = None
+    if not args.no_strong:
+        strong = {}
+        for name, gb in STRONG.items():
+            strong[name] = strong_leg(name, gb, world, rank, dev, 5 if name == "lattice" else 10, dist, torch,
+                                      core, sharding, wl)
+
+    host = {"cpus_allowed": len(os.sched_getaffinity(0)), "bound_to_gpu_numa_node": bound,
+            "gpu_numa_node": None if numa is None else numa[0]}
     if rank == 0:
         peak, peak_kind = peaks()
         achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9  # this rank's call; ranks are symmetric
-        traffic = (None if TRAFFIC_PER_ALGORITHMIC_BYTE is None
-                   else float(TRAFFIC_PER_ALGORITHMIC_BYTE * alg_bytes))
+        traffic = MEASURED_TRAFFIC.get((args.workload, batch.B))
         line = {
             "metric": "fbw fwd+bwd frames/s", "value": value, "unit": "frames/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "T": batch.T, "B_per_gpu": batch.B,
-                       "B_global": global_b, "F": batch.F, "edges_per_gpu": batch.num_edges,
-                       "states_per_gpu": batch.num_states, "partition": "by sequence, length-balanced",
-                       "l2": f"inputs ({am_bytes / 1e9:.2f} GB of scores per call) exceed the 126 MB L2; no flush"
-                             if am_bytes > 2 * 126e6 else "an L2 flush (256 MB write) runs between timed steps",
-                       "step": "prepare + run per call (automata re-sorted every step)"},
+            "config": config_of(args.workload, batch, global_b),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                         "traffic_note": ("dram__bytes_read.sum + dram__bytes_write.sum over the kernels of one "
+                                          "call, ncu capture of this workload and batch size") if traffic else
+                                         "no ncu capture of this workload at this batch size",
                          "algorithmic_bytes_per_call": int(alg_bytes),
                          "scope": "whole op call (all kernels), per GPU"},
             "kernels_ms": {"prepare": prep_ms, "gather": float(phase[0]), "sweep": float(phase[1]),
@@ -560,6 +739,11 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
             "e2e": e2e,
+            "e2e_copy": e2e_copy,
+            "e2e_out_on_device": e2e_dev_out,
+            "reference_gpu_op": reference_gpu_op,
+            "strong": strong,
+            "host": host,
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

@@ -832,6 +832,9 @@ struct RunArgs {
     // caller's tensor, i6_native_ops/fbw/__init__.py:66) and `out` receives the gradient with respect
     // to it, -posterior in (B,T,F) with zeros elsewhere (what __init__.py:41-44 and autograd produce)
     int fused;
+    // 1: `out` is pinned host memory the device writes over the bus; the output pass then stores its
+    // segments with plain 16-byte vector stores instead of bulk copies from shared memory
+    int out_plain;
 };
 
 // chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
@@ -1373,6 +1376,16 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
                     n = __popc(__ballot_sync(0xffffffffu, in));
                     dlo += n;
                 } while (n == 32);
+            }
+            if (a.out_plain) {  // uniform: destination in host memory
+                __syncwarp();
+                const float4* s4 = reinterpret_cast<const float4*>(seg);
+                float4* d4 = reinterpret_cast<float4*>(row + cs);
+                const int nv = (int)((ce - cs) >> 2);
+                for (int i = lane; i < nv; i += 32) d4[i] = s4[i];
+                __syncwarp();
+                which ^= 1;
+                continue;
             }
             // make the generic-proxy writes visible to the async proxy, then one lane issues
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -2001,6 +2014,11 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             host_scores = attr.type == cudaMemoryTypeHost;
         } else {
             (void)cudaGetLastError();  // an unregistered pointer is not an error here
+        }
+        if (cudaPointerGetAttributes(&attr, out) == cudaSuccess) {
+            a.out_plain = attr.type == cudaMemoryTypeHost ? 1 : 0;
+        } else {
+            (void)cudaGetLastError();
         }
     }
     int G = ev ? 1 : choose_groups(s);

@@ -162,11 +162,13 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
 // not copied to the device as a whole; the gather kernel reads the scores the automata need (one
 // 32-byte sector per distinct (frame, sequence, emission)) straight out of host memory through the
 // unified address space, which moves a fraction of the tensor over the bus.  Everything else, and the
-// results, are those of fbw().  No counterpart in the reference, which requires CUDA tensors
-// (fbw_torch.cpp:19-23).
+// results, are those of fbw().  With `out_pinned` the (T,B,F) result is written into that pinned host
+// tensor by the output pass itself (no device copy of it exists); sums and loss2 stay on the device.
+// No counterpart in the reference, which requires CUDA tensors (fbw_torch.cpp:19-23).
 std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tensor& edges,
                                            torch::Tensor& weights, torch::Tensor& start_end_states,
-                                           torch::Tensor& seq_lens, int64_t num_states) {
+                                           torch::Tensor& seq_lens, int64_t num_states,
+                                           c10::optional<torch::Tensor> out_pinned) {
     TORCH_CHECK(!am_scores.is_cuda() && am_scores.is_pinned(),
                 "am_scores must be a pinned host tensor (use fbw() for CUDA tensors)");
     TORCH_CHECK(am_scores.is_contiguous() && am_scores.scalar_type() == torch::kFloat32,
@@ -177,7 +179,17 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
                 "start_end_states must have shape (2, B) with B = am_scores.size(1)");
     c10::cuda::CUDAGuard guard(edges.device());
     auto dev_opts = weights.options();  // float32 on the automata's device
-    torch::Tensor out  = torch::empty(am_scores.sizes(), dev_opts);
+    torch::Tensor out;
+    if (out_pinned.has_value()) {
+        // the (T,B,F) result goes straight into the caller's pinned host tensor: the output pass
+        // writes it over the bus while the gather reads scores in the other direction
+        out = *out_pinned;
+        TORCH_CHECK(!out.is_cuda() && out.is_pinned() && out.is_contiguous() &&
+                        out.scalar_type() == torch::kFloat32 && out.sizes() == am_scores.sizes(),
+                    "out must be a pinned contiguous float32 host tensor of the shape of am_scores");
+    } else {
+        out = torch::empty(am_scores.sizes(), dev_opts);
+    }
     torch::Tensor sums = torch::empty({am_scores.size(0), am_scores.size(1)}, dev_opts);
     Prepared p = prepare_impl(edges, weights, start_end_states, seq_lens, am_scores.size(0),
                               am_scores.size(2), num_states);
@@ -355,7 +367,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("fbw", &fbw, "Fast Baum-Welch CUDA routine (B200)");
     m.def("fbw_fused", &fbw_fused, "fbw on (B,T,F) log_probs, returning the gradient directly");
     m.def("fbw_host_scores", &fbw_host_scores,
-          "fbw on scores in pinned host memory: only the scores the automata need cross the bus");
+          "fbw on scores in pinned host memory: only the scores the automata need cross the bus; "
+          "`out`: optional pinned host tensor that receives the (T,B,F) result directly",
+          py::arg("am_scores"), py::arg("edges"), py::arg("weights"), py::arg("start_end_states"),
+          py::arg("seq_lens"), py::arg("num_states"), py::arg("out") = py::none());
     m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
     m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
     m.def("abi_version", []() { return fbw_b200_abi_version(); });

@@ -107,9 +107,10 @@ def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
     return out, sums, loss2, plan
 
 
-def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None):
+def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None, out=None):
     """:func:`sharded_fbw` for scores that live in pinned host memory: the op reads the scores it needs
-    in place (no copy of the whole tensor to the device).  Returns (out, sums, loss2_global).  An empty
+    in place (no copy of the whole tensor to the device); ``out``, if given, is a pinned host tensor
+    that receives the (T,B,F) result directly.  Returns (out, sums, loss2_global).  An empty
     shard is handled as in :func:`sharded_fbw`."""
     num_states, edges, weights, start_end = fsa
     if am_scores_pinned.shape[1] == 0:
@@ -119,6 +120,6 @@ def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None):
     from .fbw import core
 
     out, sums, loss2 = core.fbw_host_scores(am_scores_pinned, edges, weights, start_end, seq_lens,
-                                            int(num_states))
+                                            int(num_states), out)
     reduce_loss(loss2, group)
     return out, sums, loss2

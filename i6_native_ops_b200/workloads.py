@@ -264,6 +264,21 @@ def make_batch(name: str, B: Optional[int] = None, seed0: int = 0,
                     blank_bias=bias, seed0=seed0)
 
 
+def take_sequences(batch: FbwBatch, indices: Sequence[int]) -> FbwBatch:
+    """The sequences ``indices`` of ``batch`` as a batch of their own (a rank's shard): sequence ids
+    become 0..n-1 in the order given, state ids are renumbered densely, per-sequence seeds and the
+    frame count T are kept, so scores and automata equal those of the full batch."""
+    from .sharding import extract_shard
+
+    idx = np.asarray(indices, dtype=np.int64)
+    S, e, w, se, sl = extract_shard(batch.num_states, batch.edges, batch.weights, batch.start_end,
+                                    batch.seq_lens, idx)
+    return FbwBatch(name=batch.name, T=batch.T, B=len(idx), F=batch.F, num_states=S, edges=e, weights=w,
+                    start_end=se, seq_lens=sl, states_per_seq=batch.states_per_seq[idx],
+                    edges_per_seq=batch.edges_per_seq[idx], seq_ids=batch.seq_ids[idx], sigma=batch.sigma,
+                    blank_bias=batch.blank_bias, seed0=batch.seed0)
+
+
 def make_scores(batch: FbwBatch, device="cpu", out=None):
     """Scores of a batch as a (T,B,F) float32 torch tensor of negative log-probabilities:
     ``-log_softmax(N(0, sigma^2) logits)`` with the blank logit biased where the workload says

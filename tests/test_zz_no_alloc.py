@@ -83,7 +83,7 @@ def test_noalloc_entry_matches_regular_entry_twice(cuda):
         assert float((torch.exp(-out.double()) - torch.exp(-ref_out.double())).abs().max()) <= POST_ATOL
         assert abs(float(loss2[0]) - float(ref_sums.double().sum())) <= 1e-5 * float(ref_sums.double().sum())
         # and against the truth: per-frame sums to 1e-5, posteriors to the fp32 rounding of the scores
-        post, loss, pattern_ok = truth_distances(b, am, [out], [sums], np.arange(b.B))
+        post, _, loss, pattern_ok = truth_distances(b, am, [out], [sums], np.arange(b.B))
         assert pattern_ok and loss.max() <= LOSS_RTOL
         assert post.max() <= 4 * max(POST_ATOL, 64 * float(sums.abs().max()) * 2.0 ** -23)
 
