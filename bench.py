@@ -422,8 +422,21 @@ def strong_leg(name, global_b, world, rank, dev, steps, dist, torch, core, shard
     batch = wl.take_sequences(full, parts[rank])
     am = wl.make_scores(batch, dev)
     fsa, seq_lens = wl.to_torch(batch, dev)
+    def op_only():
+        plan = core.fbw_prepare(fsa[1], fsa[2], fsa[3], seq_lens, batch.T, batch.F, int(fsa[0]))
+        return core.fbw_run(plan, am)
+
     for _ in range(3):
         sharding.sharded_fbw(am, fsa, seq_lens)
+    # this rank's own work, without the collective: shows how well the partition balances the ranks
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        op_only()
+    e1.record()
+    torch.cuda.synchronize()
+    local_ms = e0.elapsed_time(e1) / steps
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -434,13 +447,17 @@ def strong_leg(name, global_b, world, rank, dev, steps, dist, torch, core, shard
         ev[i + 1].record()
     torch.cuda.synchronize()
     mine = ev[0].elapsed_time(ev[steps]) / steps
-    t = torch.tensor([mine], device=dev, dtype=torch.float64)
-    all_ms = [torch.zeros_like(t) for _ in range(world)]
-    if world > 1:
-        dist.all_gather(all_ms, t)
-    else:
-        all_ms = [t]
-    rank_ms = [float(x.item()) for x in all_ms]
+
+    def gather(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world == 1:
+            return [float(x)]
+        got = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(got, t)
+        return [float(g.item()) for g in got]
+
+    rank_ms = gather(mine)
+    rank_local_ms = gather(local_ms)
     ms = max(rank_ms)
     alg = full.algorithmic_bytes()
     peak, _ = peaks()
@@ -448,7 +465,11 @@ def strong_leg(name, global_b, world, rank, dev, steps, dist, torch, core, shard
     torch.cuda.empty_cache()
     return {"B_global": int(global_b), "B_per_rank": [int(len(p)) for p in parts], "T": int(full.T),
             "F": int(full.F), "steps": steps, "ms_per_step": ms, "frames_per_s": full.T * global_b / (ms * 1e-3),
-            "rank_ms": rank_ms, "cost_imbalance": float(loads.max() / loads.mean()),
+            "rank_ms": rank_ms, "rank_op_ms": rank_local_ms,
+            "rank_frames": [int(batch_frames) for batch_frames in
+                            [full.seq_lens[p].astype(np.int64).sum() for p in parts]],
+            "rank_max_states": [int(full.states_per_seq[p].max()) if len(p) else 0 for p in parts],
+            "cost_imbalance": float(loads.max() / loads.mean()),
             "roofline_frac_per_gpu": alg / world / (ms * 1e-3) / 1e9 / peak,
             "scaling": "strong"}
 

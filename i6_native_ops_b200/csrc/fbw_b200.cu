@@ -835,6 +835,9 @@ struct RunArgs {
     // 1: `out` is pinned host memory the device writes over the bus; the output pass then stores its
     // segments with plain 16-byte vector stores instead of bulk copies from shared memory
     int out_plain;
+    // 1: the sweeps compute every state's score, also of states that cannot lie on a complete path
+    // (the debug export of the forward scores then equals the reference's buffer everywhere)
+    int keep_dead_states;
 };
 
 // chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
@@ -931,7 +934,17 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
 // Replaces set_start_states / init_bwd_state_buffer / next_frame / fill_array and the two host loops
 // (fbw_op.cu:17-29, 61-102, 297-353).
 // KREG: edges of a thread's state kept in registers (further edges are read from the list).
-template <int RING, bool TILED, int KREG>
+// prune != 0 (large automata): states that cannot lie on a complete path are skipped.  At set-up the
+// CTA finds, by a breadth-first search over its edge list, the smallest number of frames each state
+// needs to reach the sequence's end state (forward sweep) or to be reached from its start state
+// (backward sweep).  A state that needs more frames than are left cannot lie on a path of exactly
+// seq_len frames: its score can only ever meet a +inf score of the other direction in an edge score,
+// so it is set to +inf without being computed.  The outputs are unchanged bit for bit; only the
+// stored state scores of such dead states differ from the reference's forward buffer
+// (RunArgs::keep_dead_states switches the skipping off for the debug export).  The states the sweep
+// itself has not reached yet (+inf sources) are skipped edge by edge as before, so per frame only the
+// band of states that are both reachable and useful costs arithmetic.
+template <int RING, bool TILED, int KREG, bool PRUNE>
 __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int item = blockIdx.x;
@@ -952,7 +965,8 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     float* ring  = reinterpret_cast<float*>(smem_raw);                      // RING * dpmax
     float* sbase = ring + (size_t)RING * dpmax;                             // kRows * spad
     int*   rp    = reinterpret_cast<int*>(sbase + (((size_t)kRows * spad + 3) & ~(size_t)3));
-    uint2* recs_s = reinterpret_cast<uint2*>(rp + ((smax + 2) & ~1));
+    unsigned short* hops = reinterpret_cast<unsigned short*>(rp + ((smax + 2) & ~1));  // if prune
+    uint2* recs_s = reinterpret_cast<uint2*>(hops + ((smax + 3) & ~3));
 
     const int* __restrict__ rowptr = (fwd ? a.rowptr_f : a.rowptr_b) + s0;
     const uint2* __restrict__ recs_g = (fwd ? a.fwd_rec : a.bwd_rec) + e0;
@@ -961,6 +975,39 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     if (edges_in_smem) {
         for (int i = tid; i < Eb; i += NT) recs_s[i] = recs_g[i];
         recs = recs_s;
+    }
+    const bool prune = PRUNE && !a.keep_dead_states;
+    if (prune) {
+        // hops[s]: fewest frames from state s to the end state (forward sweep: the edge list is sorted
+        // by target, so a settled state relaxes the sources of its in-edges) or from the start state
+        // to s (backward sweep: list sorted by source, a settled state relaxes its targets).
+        // Level-synchronous: one round per hop count, until a round settles nothing new.
+        __shared__ int settled;
+        const int far = 0xffff;
+        const int origin = fwd ? a.end_l[b] : a.start_l[b];
+        for (int s = tid; s < Sb; s += NT) hops[s] = (unsigned short)(s == origin ? 0 : far);
+        __syncthreads();
+        for (int level = 0; level < far - 1; level++) {
+            if (tid == 0) settled = 0;
+            __syncthreads();
+            bool any = false;
+            for (int s = tid; s < Sb; s += NT) {
+                if (hops[s] == level) {
+                    const int i1 = rp[s + 1];
+                    for (int i = rp[s]; i < i1; i++) {
+                        const int o = (int)(recs[i].x & 0xffffu);
+                        if (hops[o] == far) {  // several writers may store the same value
+                            hops[o] = (unsigned short)(level + 1);
+                            any = true;
+                        }
+                    }
+                }
+            }
+            if (any) settled = 1;
+            __syncthreads();
+            if (settled == 0) break;  // uniform: read after the barrier, written before it
+            __syncthreads();
+        }
     }
     const int step = fwd ? 1 : -1;
     const int t_first = fwd ? 0 : Te - 1;
@@ -1052,7 +1099,14 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             float* nxt = srow(j + 1, t + step);
             const float* g = RING > 0 ? ring + (size_t)(j % (RING > 0 ? RING : 1)) * dpmax
                                       : gf + (i64)t * Dp;
-            if (tid < Sb) {
+            // frames left after this step for the state just computed: forward, alpha_{j+1} has
+            // Te - (j+1) frames to reach the end; backward, beta at frame t must be reached from the
+            // start in t frames.  A state that needs more is dead (see above).
+            const int left = fwd ? Te - 1 - j : t;
+            if (PRUNE && tid < Sb && prune && (int)hops[tid] > left) {
+                nxt[tid] = CUDART_INF_F;
+                if (hand) carry[tid] = CUDART_INF_F;
+            } else if (tid < Sb) {
                 // An unreachable source state (+inf) or a padding entry (weight +inf) gives +inf by
                 // itself, and prob_add treats +inf terms exactly (a + inf term leaves the sum as it
                 // is, a sum that is still +inf takes the term), so the register part needs no tests.
@@ -1074,7 +1128,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             }
             for (int s = tid + NT; s < Sb; s += NT) {
                 float acc = CUDART_INF_F;
-                const int i1 = rp[s + 1];
+                const int i1 = (PRUNE && prune && (int)hops[s] > left) ? 0 : rp[s + 1];
                 for (int i = rp[s]; i < i1; i++) {
                     const uint2 r  = recs[i];
                     const float pv = cur[r.x & 0xffffu];
@@ -1264,6 +1318,7 @@ __global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
         }
     }
 }
+
 
 // Stream the (T,B,F) output: every row is +inf except the sequence's class slots, which get the
 // posteriors k_post left in P (frame-major, ascending emission id); rows at or past seq_len are all
@@ -1567,12 +1622,12 @@ std::atomic<long long> g_launches{0};
         }                                        \
     } while (0)
 
-template <int RING, bool TILED, int KREG>
+template <int RING, bool TILED, int KREG, bool PRUNE>
 int launch_sweep_k(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
                    int edges_in_smem, cudaStream_t st) {
     static std::atomic<int> granted[kMaxDevices];
-    CUDA_OK(grant_smem(k_sweep<RING, TILED, KREG>, granted, smem));
-    k_sweep<RING, TILED, KREG><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    CUDA_OK(grant_smem(k_sweep<RING, TILED, KREG, PRUNE>, granted, smem));
+    k_sweep<RING, TILED, KREG, PRUNE><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
     COUNT_LAUNCH(1);
     return FBW_B200_OK;
 }
@@ -1580,9 +1635,41 @@ int launch_sweep_k(const RunArgs& a, int grid, int nt, size_t smem, int smax, in
 template <int RING, bool TILED>
 int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
                  int edges_in_smem, int degree, cudaStream_t st) {
-    if (degree <= 2) return launch_sweep_k<RING, TILED, 2>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
-    if (degree <= 3) return launch_sweep_k<RING, TILED, 3>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
-    return launch_sweep_k<RING, TILED, 4>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    // skipping dead states pays for its set-up where a state has many edges or a thread several states
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("FBW_B200_PRUNE"); forced = e ? atoi(e) : 2; }
+    const int prune = forced == 2 ? (degree >= 6 ? 1 : 0) : forced;
+    // (the pruning variant exists for the four-register kernel only: automata with at most three
+    // edges per state are chains, where almost every state is alive almost all of the time)
+    if (degree <= 2) return launch_sweep_k<RING, TILED, 2, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    if (degree <= 3) return launch_sweep_k<RING, TILED, 3, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    if (prune) return launch_sweep_k<RING, TILED, 4, true>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    return launch_sweep_k<RING, TILED, 4, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+}
+
+#include "sweep_cluster_b200.inc"
+// CTAs per cluster for the sweeps of `items` (sequence, direction) pairs of automata of at most ms
+// states, when `spare` SMs would otherwise stay idle during the call's sweeps.  A cluster spreads the
+// per-frame work of one large sequence over several SMs, which shortens the call only while SMs are
+// free: a call that already has a sweep CTA for every SM gains nothing and pays for the cluster
+// barriers.  Returns 1, 2 or 4 and takes the SMs it uses off `spare`.  FBW_B200_CLUSTER=1|2|4 fixes
+// the answer.
+int sweep_cluster_size(i64 ms, int items, int* spare) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("FBW_B200_CLUSTER");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced == 1 || forced == 2 || forced == 4) return forced;
+    if (ms <= 1024 || items <= 0) return 1;
+    for (int cs = ms > 2048 ? 4 : 2; cs > 1; cs >>= 1) {
+        const int extra = (cs - 1) * items;
+        if (extra <= *spare) {
+            *spare -= extra;
+            return cs;
+        }
+    }
+    return 1;
 }
 
 constexpr int kMaxChunks = 16;
@@ -1685,7 +1772,8 @@ SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
         const size_t spad = tiled ? (size_t)(c.smax | 1) : (size_t)c.smax;
         const size_t rows = tiled ? 64 : 2;
         return (size_t)4 * ring * c.dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
-               (size_t)4 * ((c.smax + 2) & ~1) + (in_smem ? (size_t)8 * me : 0) + 16;
+               (size_t)4 * ((c.smax + 2) & ~1) + (size_t)2 * ((c.smax + 3) & ~3) +
+               (in_smem ? (size_t)8 * me : 0) + 16;
     };
     for (int es = 1; es >= 0 && !c.found; es--) {
         for (int tl = 1; tl >= 0 && !c.found; tl--) {
@@ -1706,7 +1794,7 @@ enum { kDoGather = 1, kDoSweep = 2, kDoPost = 4, kDoExpand = 8, kDoAll = 15 };
 
 // `what` selects the stages to launch (the time-chunked pipeline launches them on different streams)
 int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b200_summary& s,
-                 cudaStream_t st, cudaEvent_t* ev, int what = kDoAll) {
+                 cudaStream_t st, cudaEvent_t* ev, int what = kDoAll, int cs = 1) {
     const int sms = sm_count();
     const int nb  = r1 - r0;
     a.r0 = r0;
@@ -1720,7 +1808,10 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         COUNT_LAUNCH(1);
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[1], st));
-    if ((what & kDoSweep) && s.max_len > 0) {
+    if ((what & kDoSweep) && s.max_len > 0 && cs > 1 && cluster_shape(ms, me, md, cs).found) {
+        const int rc = launch_sweepc(a, cluster_shape(ms, me, md, cs), 2 * nb, st);
+        if (rc != FBW_B200_OK) return rc;
+    } else if ((what & kDoSweep) && s.max_len > 0) {
         const SweepShape c = sweep_shape(ms, me, md);
         if (!c.found) return FBW_B200_TOO_LARGE;
         const int smax = c.smax, dpmax = c.dpmax, nt = c.nt, ring = c.ring, tiled = c.tiled;
@@ -1754,11 +1845,11 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
     if ((what & kDoPost) && s.post_units > 0) {
         const i64 units = tiles * nb;  // upper bound; the kernels read the exact count
         int g1 = (int)(units < (i64)sms * 8 ? units : (i64)sms * 8);
-        k_score<<<g1 > 0 ? g1 : 1, 256, 0, st>>>(a);
         i64 w2 = (units + 3) / 4;
         int g2 = (int)(w2 < (i64)sms * 16 ? w2 : (i64)sms * 16);
-        k_norm<<<g2 > 0 ? g2 : 1, 128, 0, st>>>(a);
         int g3 = (int)(units < (i64)sms * 12 ? units : (i64)sms * 12);
+        k_score<<<g1 > 0 ? g1 : 1, 256, 0, st>>>(a);
+        k_norm<<<g2 > 0 ? g2 : 1, 128, 0, st>>>(a);
         k_class<<<g3 > 0 ? g3 : 1, 128, 0, st>>>(a);
         COUNT_LAUNCH(3);
     }
@@ -1980,7 +2071,7 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
 
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
-                    fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0) {
+                    fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0) {
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -1989,6 +2080,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     if (work_bytes < R.total) return FBW_B200_WORKSPACE;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     RunArgs a = fbw_args(plan, s, work, R, am, out, sums, loss2, fused);
+    a.keep_dead_states = keep_dead_states;
 
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
@@ -2043,8 +2135,29 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         // expensive groups are still sweeping (FBW_B200_GROUP_ORDER=0: most expensive first)
         static int reverse = -1;
         if (reverse < 0) { const char* e = getenv("FBW_B200_GROUP_ORDER"); reverse = e ? atoi(e) : 1; }
+        // Clusters for the groups of the largest automata, most expensive group first, while the
+        // call's sweep CTAs stay below one and a half per SM (the CTAs of short sequences leave
+        // early; measured on 64 lattice sequences: 24.6 ms without clusters, 18.6 ms filling the
+        // idle SMs only, 15.0 ms with this bound, 16.4 ms with two CTAs per SM).
+        int group_cs[FBW_B200_GROUPS];
+        bool clustered = false;
+        {
+            static double oversub = -1.0;
+            if (oversub < 0) { const char* e = getenv("FBW_B200_CLUSTER_OVERSUB"); oversub = e ? atof(e) : 0.5; }
+            int spare = (int)(sm_count() * (1.0 + oversub)) - 2 * (int)s.B;
+            for (int g = 0; g < G; g++) {
+                const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
+                const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
+                i64 gs_ = 0;
+                for (int q = g * per; q < (g + 1) * per; q++) gs_ = s.group_max_states[q] > gs_ ? s.group_max_states[q] : gs_;
+                group_cs[g] = sweep_cluster_size(gs_, 2 * (r1 - r0), &spare);
+                clustered = clustered || group_cs[g] > 1;
+            }
+        }
+        // with clusters the long sequences are the critical path: they start first
+        const bool cheapest_first = reverse && !clustered;
         for (int gi = 0; gi < G; gi++) {
-            const int g = reverse ? G - 1 - gi : gi;
+            const int g = cheapest_first ? G - 1 - gi : gi;
             const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
             const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
             if (r1 <= r0) continue;
@@ -2059,7 +2172,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
                 rc_forked = FBW_B200_CUDA_ERROR;
                 break;
             }
-            int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll);
+            int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll, group_cs[g]);
             if (gi > 0 && (cudaEventRecord(pool->join[gi], gstream) != cudaSuccess ||
                            cudaStreamWaitEvent(st, pool->join[gi], 0) != cudaSuccess)) {
                 rc = rc != FBW_B200_OK ? rc : FBW_B200_CUDA_ERROR;
@@ -2084,10 +2197,12 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             if (e != cudaSuccess && rc_forked == FBW_B200_OK) rc_forked = FBW_B200_CUDA_ERROR;
             return rc_forked == FBW_B200_OK;
         };
+        int spare = sm_count() - 2 * (int)s.B;
+        const int cs_all = sweep_cluster_size(ms, 2 * (int)s.B, &spare);
         auto stage = [&](int c, cudaStream_t on, int what) {
             a.c_lo = c;
             a.c_hi = c + 1;
-            const int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, on, nullptr, what);
+            const int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, on, nullptr, what, cs_all);
             if (rc != FBW_B200_OK && rc_forked == FBW_B200_OK) rc_forked = rc;
             return rc_forked == FBW_B200_OK;
         };
@@ -2121,7 +2236,9 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             }
         }
     } else {
-        int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kDoAll);
+        int spare = sm_count() - 2 * (int)s.B;
+        int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kDoAll,
+                              sweep_cluster_size(ms, 2 * (int)s.B, &spare));
         if (rc != FBW_B200_OK) return rc;
     }
     if (rc_forked != FBW_B200_OK) return rc_forked;
@@ -2145,6 +2262,12 @@ int fbw_b200_run_fused(const void* plan, const fbw_b200_summary* summary, const 
                        float* grad, float* sums, float* loss2, void* work, size_t work_bytes,
                        fbw_b200_stream_t stream) {
     return run_impl(plan, summary, log_probs, grad, sums, loss2, work, work_bytes, stream, nullptr, 1);
+}
+
+int fbw_b200_run_for_export(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                            float* sums, float* loss2, void* work, size_t work_bytes,
+                            fbw_b200_stream_t stream) {
+    return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 1);
 }
 
 int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,
@@ -2252,7 +2375,9 @@ int fbw_b200_fbw_noalloc(const float* am, const int32_t* edges, const float* wei
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(sum.T * sum.B), st));
     i64 ms, me, md;
     plan_maxima(sum, ms, me, md);
-    rc = launch_group(a, 0, (int)sum.B, ms, me, md, sum, st, nullptr, kDoAll);  // one stream, one chunk
+    int spare = sm_count() - 2 * (int)sum.B;
+    rc = launch_group(a, 0, (int)sum.B, ms, me, md, sum, st, nullptr, kDoAll,   // one stream, one chunk
+                      sweep_cluster_size(ms, 2 * (int)sum.B, &spare));
     if (rc != FBW_B200_OK) return rc;
     if (loss2) {
         k_loss<<<1, 1024, 0, st>>>(sums, sum.T, sum.B, loss2);

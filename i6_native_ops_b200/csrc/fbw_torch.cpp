@@ -44,7 +44,7 @@ namespace {
 std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_scores,
                                     bool want_loss, torch::Tensor out = torch::Tensor(),
                                     torch::Tensor sums = torch::Tensor(),
-                                    torch::Tensor* work_out = nullptr) {
+                                    torch::Tensor* work_out = nullptr, bool for_export = false) {
     auto stream = at::cuda::getCurrentCUDAStream();
     const fbw_b200_summary& s = p.summary;
     if (!out.defined()) out = torch::empty_like(am_scores);
@@ -53,10 +53,11 @@ std::vector<torch::Tensor> run_impl(const Prepared& p, const torch::Tensor& am_s
     if (want_loss) loss2 = torch::empty({2}, am_scores.options());
     size_t wbytes = fbw_b200_run_bytes(&s);
     torch::Tensor work = byte_buffer(wbytes, am_scores.device());
-    check_status(fbw_b200_run(p.plan.data_ptr(), &s, am_scores.data_ptr<float>(),
-                              out.data_ptr<float>(), sums.data_ptr<float>(),
-                              want_loss ? loss2.data_ptr<float>() : nullptr, work.data_ptr(),
-                              wbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    // a call whose forward scores will be dumped computes them for every state, as the reference does
+    auto run = for_export ? fbw_b200_run_for_export : fbw_b200_run;
+    check_status(run(p.plan.data_ptr(), &s, am_scores.data_ptr<float>(), out.data_ptr<float>(),
+                     sums.data_ptr<float>(), want_loss ? loss2.data_ptr<float>() : nullptr,
+                     work.data_ptr(), wbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
     if (work_out) *work_out = work;
     if (want_loss) return {out, sums, loss2};
     return {out, sums};
@@ -143,7 +144,7 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
     const unsigned call_idx = call_counter.fetch_add(1);
     const bool dump_now = debug_options.dump_every > 0 && call_idx % debug_options.dump_every == 0;
     torch::Tensor work;
-    auto result = run_impl(p, am_scores, false, out, sums, &work);
+    auto result = run_impl(p, am_scores, false, out, sums, &work, dump_now && debug_options.dump_alignment);
     if (dump_now && debug_options.dump_alignment) {
         auto stream = at::cuda::getCurrentCUDAStream();
         torch::Tensor alpha = torch::empty({p.summary.T, p.summary.S}, am_scores.options());

@@ -121,6 +121,15 @@ int fbw_b200_run(const void* plan, const fbw_b200_summary* summary, const float*
                  float* sums, float* loss2, void* work, size_t work_bytes,
                  fbw_b200_stream_t stream);
 
+/* fbw_b200_run for a call whose forward state scores will be exported (fbw_b200_export_alpha): same
+ * arguments, same `out` and `sums` bit for bit.  The plain run leaves at +inf the scores of states
+ * that cannot lie on a complete path (too few frames left to reach the end state), which no output
+ * depends on; this variant computes them as the reference does (fbw_op.cu:71-102 relaxes every edge),
+ * so that the exported forward scores equal the reference's state buffer (fbw_op.cu:304-315). */
+int fbw_b200_run_for_export(const void* plan, const fbw_b200_summary* summary, const float* am,
+                            float* out, float* sums, float* loss2, void* work, size_t work_bytes,
+                            fbw_b200_stream_t stream);
+
 /* fbw_b200_run with the Python wrapper's elementwise passes folded in (the steps either side of the
  * op in i6_native_ops/fbw/__init__.py:41-44 and :66): the input is log_probs in the caller's own
  * (B,T,F) layout and sign (prepare was given T, B, F of that tensor), the output `grad` (B,T,F) is
