@@ -1150,6 +1150,9 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
 }
 
 constexpr int kPostBatch = 8;  // edges whose lines are loaded together
+// lines of edge scores a k_norm warp keeps in flight beyond the ones it is folding: the fold is a
+// chain of dependent steps fed from DRAM, and its only parallelism is how far ahead it loads
+constexpr int kNormBatch = 16;
 
 // decode a work unit (sequence, 32-frame tile) from its index in rank order
 struct PostUnit {
@@ -1229,20 +1232,20 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
         const bool valid = t < p.Te;
         const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
         float acc = CUDART_INF_F;
-        float nx[kPostBatch];
+        float nx[kNormBatch];
 #pragma unroll
-        for (int j = 0; j < kPostBatch; j++) nx[j] = j < p.Eb ? Xb[(i64)j * kTile] : CUDART_INF_F;
-        for (int i0 = 0; i0 < p.Eb; i0 += kPostBatch) {
-            float x[kPostBatch];
+        for (int j = 0; j < kNormBatch; j++) nx[j] = j < p.Eb ? Xb[(i64)j * kTile] : CUDART_INF_F;
+        for (int i0 = 0; i0 < p.Eb; i0 += kNormBatch) {
+            float x[kNormBatch];
 #pragma unroll
-            for (int j = 0; j < kPostBatch; j++) x[j] = nx[j];
+            for (int j = 0; j < kNormBatch; j++) x[j] = nx[j];
 #pragma unroll
-            for (int j = 0; j < kPostBatch; j++) {
-                const int i = i0 + kPostBatch + j;
+            for (int j = 0; j < kNormBatch; j++) {
+                const int i = i0 + kNormBatch + j;
                 nx[j] = i < p.Eb ? Xb[(i64)i * kTile] : CUDART_INF_F;
             }
 #pragma unroll
-            for (int j = 0; j < kPostBatch; j++) acc = prob_add_fast(acc, x[j]);
+            for (int j = 0; j < kNormBatch; j++) acc = prob_add_fast(acc, x[j]);
         }
         if (valid) a.sums[(i64)t * a.B + p.b] = isinf(acc) ? 0.f : acc;
         a.N[p.u * kTile + lane] = acc;
