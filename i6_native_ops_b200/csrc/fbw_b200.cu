@@ -1870,7 +1870,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
 
 extern "C" {
 
-int fbw_b200_abi_version(void) { return 2; }
+int fbw_b200_abi_version(void) { return 3; }
 
 const char* fbw_b200_status_string(int status) {
     switch (status) {

@@ -18,7 +18,7 @@ import sys
 
 
 def default_reference_root() -> str:
-    """Where the reference checkout lies: $I6_NATIVE_OPS_REFERENCE, else /root/reference."""
+    """Where the reference checkout lies: $I6_NATIVE_OPS_REFERENCE, else the default below."""
     return os.environ.get("I6_NATIVE_OPS_REFERENCE", "/root/reference")
 
 
