@@ -945,7 +945,8 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
 // itself has not reached yet (+inf sources) are skipped edge by edge as before, so per frame only the
 // band of states that are both reachable and useful costs arithmetic.
 template <int RING, bool TILED, int KREG, bool PRUNE>
-__global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem) {
+__global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem,
+                                                int nrows) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int item = blockIdx.x;
     const int b    = a.order[a.r0 + (item >> 1)];  // most expensive sequences first
@@ -958,7 +959,9 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     const int Dp = (Db + 3) & ~3;
     const int NT = blockDim.x, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
-    constexpr int kRows = TILED ? 64 : 2;
+    // state vectors kept in shared memory: 64 (TILED), else nrows = 2 or 4.  With four, the vectors of
+    // four consecutive frames leave as one 16-byte store per state instead of four 4-byte stores.
+    const int kRows = TILED ? 64 : nrows;
     constexpr int kRegEdges = KREG;
     const int spad = TILED ? (smax | 1) : smax;  // odd row stride: conflict-free transposed reads
 
@@ -1012,7 +1015,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     const int step = fwd ? 1 : -1;
     const int t_first = fwd ? 0 : Te - 1;
     auto srow = [&](int j, int t) -> float* {
-        return sbase + (size_t)(TILED ? (t & 63) : (j & 1)) * spad;
+        return sbase + (size_t)(TILED ? (t & 63) : (j & (kRows - 1))) * spad;
     };
     // this launch covers steps [j0, j1) of the sequence's Te steps (a time chunk); a later chunk
     // picks up the state vector the previous one left in `carry`
@@ -1089,9 +1092,37 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
         __syncthreads();
         if (RING > 0) issue(j + RING - 1);
         const float* cur = srow(j, t);
-        if (!TILED) {  // record this frame's state scores (tiled layout: [t/32][state][t%32])
+        if (!TILED && kRows == 2) {  // record this frame's state scores (tiled layout: [t/32][state][t%32])
             float* drow = dst + ((i64)(t >> 5) * Sb) * kTile + (t & 31);
             for (int s = tid; s < Sb; s += NT) drow[(i64)s * kTile] = cur[s];
+        } else if (!TILED) {
+            // Four rows: the vectors of steps j-3 .. j are in shared memory.  When the sweep leaves an
+            // aligned group of four frames (or the launch ends) the frames of that group recorded by
+            // this launch are written, as one float4 per state if all four are there.  Every thread
+            // reads only its own states' entries, which only itself overwrites (after this).
+            const bool group_end  = fwd ? ((t & 3) == 3) : ((t & 3) == 0);
+            const bool launch_end = j == j1 - 1;
+            if (group_end || launch_end) {
+                const int first = t_first + step * j0;  // first frame this launch recorded
+                const int g0 = t & ~3;
+                const int lo = fwd ? max(g0, first) : t;
+                const int hi = fwd ? t : min(g0 + 3, first);
+                float* base = dst + ((i64)(t >> 5) * Sb) * kTile + (g0 & 31);
+                auto row_of = [&](int f) -> const float* {  // vector of frame f: step f or Te-1-f
+                    return sbase + (size_t)((fwd ? f : Te - 1 - f) & 3) * spad;
+                };
+                if (lo == g0 && hi == g0 + 3) {
+                    const float *r0 = row_of(g0), *r1 = row_of(g0 + 1), *r2 = row_of(g0 + 2), *r3 = row_of(g0 + 3);
+                    for (int s = tid; s < Sb; s += NT) {
+                        *reinterpret_cast<float4*>(base + (i64)s * kTile) = make_float4(r0[s], r1[s], r2[s], r3[s]);
+                    }
+                } else {
+                    for (int f = lo; f <= hi; f++) {
+                        const float* r = row_of(f);
+                        for (int s = tid; s < Sb; s += NT) base[(i64)s * kTile + (f - g0)] = r[s];
+                    }
+                }
+            }
         }
         const bool last  = j == Te - 1;           // the sequence ends here: nothing to compute
         const bool hand  = j == j1 - 1 && !last;  // a later chunk continues from the next vector
@@ -1627,27 +1658,27 @@ std::atomic<long long> g_launches{0};
 
 template <int RING, bool TILED, int KREG, bool PRUNE>
 int launch_sweep_k(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
-                   int edges_in_smem, cudaStream_t st) {
+                   int edges_in_smem, int nrows, cudaStream_t st) {
     static std::atomic<int> granted[kMaxDevices];
     CUDA_OK(grant_smem(k_sweep<RING, TILED, KREG, PRUNE>, granted, smem));
-    k_sweep<RING, TILED, KREG, PRUNE><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem);
+    k_sweep<RING, TILED, KREG, PRUNE><<<grid, nt, smem, st>>>(a, smax, dpmax, edges_in_smem, nrows);
     COUNT_LAUNCH(1);
     return FBW_B200_OK;
 }
 
 template <int RING, bool TILED>
 int launch_sweep(const RunArgs& a, int grid, int nt, size_t smem, int smax, int dpmax,
-                 int edges_in_smem, int degree, cudaStream_t st) {
+                 int edges_in_smem, int nrows, int degree, cudaStream_t st) {
     // skipping dead states pays for its set-up where a state has many edges or a thread several states
     static int forced = -1;
     if (forced < 0) { const char* e = getenv("FBW_B200_PRUNE"); forced = e ? atoi(e) : 2; }
     const int prune = forced == 2 ? (degree >= 6 ? 1 : 0) : forced;
     // (the pruning variant exists for the four-register kernel only: automata with at most three
     // edges per state are chains, where almost every state is alive almost all of the time)
-    if (degree <= 2) return launch_sweep_k<RING, TILED, 2, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
-    if (degree <= 3) return launch_sweep_k<RING, TILED, 3, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
-    if (prune) return launch_sweep_k<RING, TILED, 4, true>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
-    return launch_sweep_k<RING, TILED, 4, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, st);
+    if (degree <= 2) return launch_sweep_k<RING, TILED, 2, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, nrows, st);
+    if (degree <= 3) return launch_sweep_k<RING, TILED, 3, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, nrows, st);
+    if (prune) return launch_sweep_k<RING, TILED, 4, true>(a, grid, nt, smem, smax, dpmax, edges_in_smem, nrows, st);
+    return launch_sweep_k<RING, TILED, 4, false>(a, grid, nt, smem, smax, dpmax, edges_in_smem, nrows, st);
 }
 
 #include "sweep_cluster_b200.inc"
@@ -1754,36 +1785,42 @@ int choose_chunks(const fbw_b200_summary& s) {
 }
 
 // Launch shape of k_sweep for automata of at most ms states, me edges and md class slots.
-// Shared memory of the kernel: score ring, state rows (64 tiled or 2), row pointers, edge records.
-// Preference: edges in shared memory, then tiled state rows, then a deep score ring.
+// Shared memory of the kernel: score ring, state rows (64 tiled, else 4 or 2), row pointers, edge
+// records.  Preference: edges in shared memory, then tiled state rows, then a score ring with four
+// state rows, a ring with two, and last no ring at all.
 struct SweepShape {
     bool   found;
-    int    ring, tiled, in_smem, smax, dpmax, nt;
+    int    ring, tiled, rows, in_smem, smax, dpmax, nt;
     size_t smem;
 };
 SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
     SweepShape c;
     c.found = false;
     c.ring = c.tiled = c.in_smem = 0;
+    c.rows = 2;
     c.smem  = 0;
     c.smax  = (int)((ms + 3) & ~3);
     c.dpmax = (int)((md + 3) & ~3);
     c.nt    = (int)((ms + 31) & ~31);
     c.nt    = c.nt < 64 ? 64 : (c.nt > 1024 ? 1024 : c.nt);
     const size_t limit = 227 * 1024;
-    auto need = [&](int ring, int tiled, int in_smem) {
-        const size_t spad = tiled ? (size_t)(c.smax | 1) : (size_t)c.smax;
-        const size_t rows = tiled ? 64 : 2;
-        return (size_t)4 * ring * c.dpmax + 4 * ((rows * spad + 3) & ~(size_t)3) +
+    auto need = [&](int ring, int rows, int in_smem) {
+        const size_t spad = rows == 64 ? (size_t)(c.smax | 1) : (size_t)c.smax;
+        return (size_t)4 * ring * c.dpmax + 4 * (((size_t)rows * spad + 3) & ~(size_t)3) +
                (size_t)4 * ((c.smax + 2) & ~1) + (size_t)2 * ((c.smax + 3) & ~3) +
                (in_smem ? (size_t)8 * me : 0) + 16;
     };
+    static int rows4 = -1;
+    if (rows4 < 0) { const char* e = getenv("FBW_B200_ROWS4"); rows4 = e ? atoi(e) : 1; }
     for (int es = 1; es >= 0 && !c.found; es--) {
-        for (int tl = 1; tl >= 0 && !c.found; tl--) {
-            for (int rg = 16; rg >= 0 && !c.found; rg = rg > 2 ? rg / 2 : rg - 2) {
-                if (need(rg, tl, es) <= limit) {
-                    c.ring = rg; c.tiled = tl; c.in_smem = es; c.found = true;
-                    c.smem = need(rg, tl, es);
+        // pass 0: 64 rows; 1: 4 rows with a ring; 2: 2 rows with a ring; 3: 4 rows, no ring; 4: 2 rows, no ring
+        for (int pass = 0; pass < 5 && !c.found; pass++) {
+            const int rows = pass == 0 ? 64 : ((pass == 1 || pass == 3) ? 4 : 2);
+            if (rows == 4 && !rows4) continue;
+            for (int rg = (pass >= 3 ? 0 : 16); rg >= (pass >= 3 || pass == 0 ? 0 : 2) && !c.found; rg = rg > 2 ? rg / 2 : rg - 2) {
+                if (need(rg, rows, es) <= limit) {
+                    c.ring = rg; c.tiled = rows == 64; c.rows = rows; c.in_smem = es; c.found = true;
+                    c.smem = need(rg, rows, es);
                 }
             }
         }
@@ -1823,7 +1860,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         const int grid = 2 * nb;
         int rc;
 #define SWEEP_CASE(R, TL) \
-    rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, (int)s.max_degree, st)
+    rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, c.rows, (int)s.max_degree, st)
         if (tiled) {
             switch (ring) {
                 case 16: SWEEP_CASE(16, true); break;
@@ -2139,14 +2176,14 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         static int reverse = -1;
         if (reverse < 0) { const char* e = getenv("FBW_B200_GROUP_ORDER"); reverse = e ? atoi(e) : 1; }
         // Clusters for the groups of the largest automata, most expensive group first, while the
-        // call's sweep CTAs stay below one and a half per SM (the CTAs of short sequences leave
-        // early; measured on 64 lattice sequences: 24.6 ms without clusters, 18.6 ms filling the
-        // idle SMs only, 15.0 ms with this bound, 16.4 ms with two CTAs per SM).
+        // call's sweep CTAs stay below 1.65 per SM (the CTAs of short sequences leave early;
+        // measured on 64 lattice sequences: 24.6 ms without clusters, 18.6 ms filling the idle SMs
+        // only, 15.0 ms with a bound of 1.5, 14.4 ms with 1.65, 14.6 ms with 1.8).
         int group_cs[FBW_B200_GROUPS];
         bool clustered = false;
         {
             static double oversub = -1.0;
-            if (oversub < 0) { const char* e = getenv("FBW_B200_CLUSTER_OVERSUB"); oversub = e ? atof(e) : 0.5; }
+            if (oversub < 0) { const char* e = getenv("FBW_B200_CLUSTER_OVERSUB"); oversub = e ? atof(e) : 0.65; }
             int spare = (int)(sm_count() * (1.0 + oversub)) - 2 * (int)s.B;
             for (int g = 0; g < G; g++) {
                 const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
