@@ -676,17 +676,18 @@ def main():
 
         def step_host_to_host():
             # scores read in place from pinned host memory by the gather (no copy of the tensor to the
-            # device); the (T,B,F) result is produced on the device and copied to pinned host memory
+            # device); the (T,B,F) result is produced on the device and its finished parts are copied
+            # to pinned host memory while the op is still running
             e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
-            out, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_)
-            out_h.copy_(out, non_blocking=True)
+            _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_, out=out_h)
             return finish(sums, loss2)
 
         def step_in_place():
             # as above, but the op's output pass writes the result straight into pinned host memory
             # (no device copy of the result exists; saves its HBM, costs bus efficiency)
             e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
-            _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_, out=out_h)
+            _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_, out=out_h,
+                                                              staged=False)
             return finish(sums, loss2)
 
         def step_copy():
@@ -725,7 +726,7 @@ def main():
         e2e = time_leg(step_host_to_host, sectors + fsa_bytes, out_bytes + small_d2h,
                        "inputs and results in pinned host memory: scores read in place by the op's gather "
                        f"(32-byte sectors of a {am_h.numel() * 4}-byte tensor), the (T,B,F) result copied "
-                       "device -> host, sums and loss copied back")
+                       "device -> host piece by piece while the op runs, sums and loss copied back")
         e2e_in_place = time_leg(step_in_place, sectors + fsa_bytes, out_bytes + small_d2h,
                                 "as e2e, but the op's output pass writes the (T,B,F) result straight into "
                                 "pinned host memory (no device copy of the result)")

@@ -1714,8 +1714,9 @@ struct StreamPool {
     std::mutex   mu;
     bool         ready = false, failed = false;
     cudaStream_t aux[FBW_B200_GROUPS];
-    cudaEvent_t  fork, join[FBW_B200_GROUPS];
-    cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks];
+    cudaStream_t copy;  // device -> host copies of finished parts of the output
+    cudaEvent_t  fork, join[FBW_B200_GROUPS], copied;
+    cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks], expanded[kMaxChunks];
 };
 StreamPool g_pools[kMaxDevices];
 std::mutex g_pools_mu;
@@ -1727,14 +1728,17 @@ StreamPool* stream_pool() {
     std::lock_guard<std::mutex> lk(g_pools_mu);
     if (p->failed) return nullptr;
     if (!p->ready) {
-        bool ok = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming) == cudaSuccess;
+        bool ok = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&p->copied, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&p->copy, cudaStreamNonBlocking) == cudaSuccess;
         for (int i = 0; i < FBW_B200_GROUPS && ok; i++) {
             ok = cudaStreamCreateWithFlags(&p->aux[i], cudaStreamNonBlocking) == cudaSuccess &&
                  cudaEventCreateWithFlags(&p->join[i], cudaEventDisableTiming) == cudaSuccess;
         }
         for (int i = 0; i < kMaxChunks && ok; i++) {
             ok = cudaEventCreateWithFlags(&p->gathered[i], cudaEventDisableTiming) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&p->swept[i], cudaEventDisableTiming) == cudaSuccess;
+                 cudaEventCreateWithFlags(&p->swept[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&p->expanded[i], cudaEventDisableTiming) == cudaSuccess;
         }
         if (!ok) {
             p->failed = true;
@@ -2111,7 +2115,8 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
 
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
-                    fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0) {
+                    fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0,
+                    float* out_host = nullptr) {
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -2185,6 +2190,14 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             static double oversub = -1.0;
             if (oversub < 0) { const char* e = getenv("FBW_B200_CLUSTER_OVERSUB"); oversub = e ? atof(e) : 0.65; }
             int spare = (int)(sm_count() * (1.0 + oversub)) - 2 * (int)s.B;
+            // up to four sweep CTAs per SM the most expensive sequences still get clusters worth 15 %
+            // more CTAs: their sweeps, not the amount of work, end the call (128 lattice sequences:
+            // 26.0 -> 17.7 ms; 256: 31.9 -> 30.6 ms; 512 sequences are better off without: 56 -> 59 ms)
+            static double share = -1.0;
+            if (share < 0) { const char* e = getenv("FBW_B200_CLUSTER_SHARE"); share = e ? atof(e) : 0.15; }
+            if (2 * s.B <= 4 * (i64)sm_count() && spare < (int)(share * 2 * (double)s.B)) {
+                spare = (int)(share * 2 * (double)s.B);
+            }
             for (int g = 0; g < G; g++) {
                 const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
                 const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
@@ -2262,11 +2275,49 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         }
         // the output stages of successive chunks go to different streams: each stage is a chain
         // of latency-bound kernels, several chunks' chains have to be in flight at once
+        bool copied_all = false;
         for (int c = 0; c < C && go; c++) {
             if (!(c == 0 || c >= first_finish)) continue;
             cudaStream_t ps = pool->aux[1 + c % kPostStreams];
             go = ok(cudaStreamWaitEvent(ps, pool->swept[c], 0)) &&
                  stage(c, ps, c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
+            if (go && out_host) {
+                // The frames of a 32-frame tile are complete for EVERY sequence once the output
+                // stages of the chunk in which the longest sequence finishes that tile have run (a
+                // shorter sequence finishes a tile no later; tiles past the longest sequence are
+                // padding, written with chunk 0).  Complete tiles are contiguous in the (T,B,F)
+                // output, so they go to the host copy while the later chunks are still computed.
+                go = ok(cudaEventRecord(pool->expanded[c], ps)) &&
+                     ok(cudaStreamWaitEvent(pool->copy, pool->expanded[c], 0));
+                const int ntT = (int)((s.T + kTile - 1) / kTile);
+                auto tile_chunk = [&](int k) -> int {
+                    const int Te = (int)s.max_len;
+                    if (k * kTile >= Te) return 0;
+                    const int last = (k * kTile + kTile - 1 < Te - 1) ? k * kTile + kTile - 1 : Te - 1;
+                    const int a1 = last / (int)J, a2 = (Te - 1 - k * kTile) / (int)J;
+                    int dc = a1 > a2 ? a1 : a2;
+                    if (dc > 0 && dc < first_finish) dc = first_finish;  // no output stages ran in between
+                    return dc;
+                };
+                for (int k = 0; k < ntT && go;) {
+                    if (tile_chunk(k) != c) { k++; continue; }
+                    int k1 = k;
+                    while (k1 < ntT && tile_chunk(k1) == c) k1++;
+                    const i64 f0 = (i64)k * kTile, f1 = (i64)k1 * kTile < s.T ? (i64)k1 * kTile : s.T;
+                    const size_t off = (size_t)f0 * (size_t)s.B * (size_t)s.F;
+                    go = ok(cudaMemcpyAsync(out_host + off, out + off, (size_t)(f1 - f0) * s.B * s.F * sizeof(float),
+                                            cudaMemcpyDeviceToHost, pool->copy));
+                    k = k1;
+                }
+                copied_all = true;
+            }
+        }
+        if (out_host && copied_all) {
+            if (cudaEventRecord(pool->copied, pool->copy) != cudaSuccess ||
+                cudaStreamWaitEvent(st, pool->copied, 0) != cudaSuccess) {
+                if (rc_forked == FBW_B200_OK) rc_forked = FBW_B200_CUDA_ERROR;
+            }
+            out_host = nullptr;  // done piecewise
         }
         // join: the gather stream and the output streams back into the caller's stream
         for (int i = 0; i <= kPostStreams; i++) {
@@ -2282,6 +2333,9 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         if (rc != FBW_B200_OK) return rc;
     }
     if (rc_forked != FBW_B200_OK) return rc_forked;
+    if (out_host) {  // schedules without time chunks: one copy behind everything
+        CUDA_OK(cudaMemcpyAsync(out_host, out, (size_t)s.T * s.B * s.F * sizeof(float), cudaMemcpyDeviceToHost, st));
+    }
     if (ev) CUDA_OK(cudaEventRecord(ev[4], st));
     if (loss2) {
         k_loss<<<1, 1024, 0, st>>>(sums, s.T, s.B, loss2);
@@ -2308,6 +2362,13 @@ int fbw_b200_run_for_export(const void* plan, const fbw_b200_summary* summary, c
                             float* sums, float* loss2, void* work, size_t work_bytes,
                             fbw_b200_stream_t stream) {
     return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 1);
+}
+
+int fbw_b200_run_host_out(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                          float* out_host, float* sums, float* loss2, void* work, size_t work_bytes,
+                          fbw_b200_stream_t stream) {
+    if (!out_host) return FBW_B200_BAD_ARGUMENT;
+    return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, out_host);
 }
 
 int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,

@@ -163,13 +163,13 @@ std::vector<torch::Tensor> fbw(torch::Tensor& am_scores, torch::Tensor& edges,
 // not copied to the device as a whole; the gather kernel reads the scores the automata need (one
 // 32-byte sector per distinct (frame, sequence, emission)) straight out of host memory through the
 // unified address space, which moves a fraction of the tensor over the bus.  Everything else, and the
-// results, are those of fbw().  With `out_pinned` the (T,B,F) result is written into that pinned host
-// tensor by the output pass itself (no device copy of it exists); sums and loss2 stay on the device.
+// results, are those of fbw().  With `out_pinned` the (T,B,F) result is delivered into that pinned host
+// tensor (see the comment inside); sums and loss2 stay on the device.
 // No counterpart in the reference, which requires CUDA tensors (fbw_torch.cpp:19-23).
 std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tensor& edges,
                                            torch::Tensor& weights, torch::Tensor& start_end_states,
                                            torch::Tensor& seq_lens, int64_t num_states,
-                                           c10::optional<torch::Tensor> out_pinned) {
+                                           c10::optional<torch::Tensor> out_pinned, bool staged) {
     TORCH_CHECK(!am_scores.is_cuda() && am_scores.is_pinned(),
                 "am_scores must be a pinned host tensor (use fbw() for CUDA tensors)");
     TORCH_CHECK(am_scores.is_contiguous() && am_scores.scalar_type() == torch::kFloat32,
@@ -180,14 +180,17 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
                 "start_end_states must have shape (2, B) with B = am_scores.size(1)");
     c10::cuda::CUDAGuard guard(edges.device());
     auto dev_opts = weights.options();  // float32 on the automata's device
-    torch::Tensor out;
+    torch::Tensor out, out_dev;
     if (out_pinned.has_value()) {
-        // the (T,B,F) result goes straight into the caller's pinned host tensor: the output pass
-        // writes it over the bus while the gather reads scores in the other direction
+        // The (T,B,F) result ends up in the caller's pinned host tensor.  staged: it is produced in
+        // a device buffer and copied out piece by piece while the rest is still being computed (the
+        // copy engine is the faster way over the bus); otherwise the output pass writes it straight
+        // into host memory and no device copy of it exists.
         out = *out_pinned;
         TORCH_CHECK(!out.is_cuda() && out.is_pinned() && out.is_contiguous() &&
                         out.scalar_type() == torch::kFloat32 && out.sizes() == am_scores.sizes(),
                     "out must be a pinned contiguous float32 host tensor of the shape of am_scores");
+        if (staged) out_dev = torch::empty(am_scores.sizes(), dev_opts);
     } else {
         out = torch::empty(am_scores.sizes(), dev_opts);
     }
@@ -199,10 +202,17 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
     torch::Tensor work  = byte_buffer(wbytes, edges.device());
     torch::Tensor loss2 = torch::empty({2}, dev_opts);
     // pinned host memory is addressable from the device under unified addressing
-    check_status(fbw_b200_run(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
-                              out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
-                              work.data_ptr(), wbytes,
-                              reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    if (out_dev.defined()) {
+        check_status(fbw_b200_run_host_out(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
+                                           out_dev.data_ptr<float>(), out.data_ptr<float>(),
+                                           sums.data_ptr<float>(), loss2.data_ptr<float>(), work.data_ptr(),
+                                           wbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    } else {
+        check_status(fbw_b200_run(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
+                                  out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
+                                  work.data_ptr(), wbytes,
+                                  reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+    }
     return {out, sums, loss2};
 }
 
@@ -371,7 +381,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "fbw on scores in pinned host memory: only the scores the automata need cross the bus; "
           "`out`: optional pinned host tensor that receives the (T,B,F) result directly",
           py::arg("am_scores"), py::arg("edges"), py::arg("weights"), py::arg("start_end_states"),
-          py::arg("seq_lens"), py::arg("num_states"), py::arg("out") = py::none());
+          py::arg("seq_lens"), py::arg("num_states"), py::arg("out") = py::none(), py::arg("staged") = true);
     m.def("fbw_prepare", &fbw_prepare, "Validate and sort a batch of automata");
     m.def("fbw_run", &fbw_run, "Run fbw on prepared automata");
     m.def("abi_version", []() { return fbw_b200_abi_version(); });

@@ -118,19 +118,21 @@ def fbw_loss_fused(log_probs, fsa, seq_lens):
     return FusedFastBaumWelchLoss.apply(log_probs.contiguous(), fsa, seq_lens)
 
 
-def fbw_host_scores(am_scores_pinned, fsa, seq_lens, out=None):
+def fbw_host_scores(am_scores_pinned, fsa, seq_lens, out=None, staged=True):
     """The op on negative log scores ``(T, B, F)`` held in PINNED HOST memory (``tensor.pin_memory()``):
     returns ``(out (T,B,F), sum_output (T,B), loss2 (2,))``.  The scores are not copied to the device as
     a whole; the gather kernel fetches the ones the automata refer to over the bus (about a quarter of
     the tensor on the triphone workload).  ``out``: an optional pinned host tensor of the same shape
-    that receives the (T,B,F) result directly -- the output pass writes it over the bus while the
-    gather reads in the other direction, so a step whose inputs and results both live in host memory
-    needs no staging copy in either direction; without it ``out`` is a new device tensor.
+    that receives the (T,B,F) result; without it ``out`` is a new device tensor.  With
+    ``staged=True`` (default) the result is produced in a temporary device buffer and every finished
+    part of it is copied to ``out`` while the rest is still being computed; with ``staged=False`` the
+    output pass writes straight into ``out`` and no device copy of the result exists (saves its HBM,
+    slower over the bus).
     ``sum_output`` and ``loss2`` are device tensors.  Results are bit-identical to ``core.fbw`` on a
     device copy.  No counterpart in the reference, whose op requires CUDA tensors."""
     num_states, edge_tensor, weight_tensor, start_end_states = fsa
     return core.fbw_host_scores(am_scores_pinned, edge_tensor, weight_tensor, start_end_states,
-                                seq_lens, int(num_states), out)
+                                seq_lens, int(num_states), out, bool(staged))
 
 
 class PlanCache:

@@ -107,10 +107,11 @@ def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
     return out, sums, loss2, plan
 
 
-def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None, out=None):
+def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None, out=None, staged=True):
     """:func:`sharded_fbw` for scores that live in pinned host memory: the op reads the scores it needs
     in place (no copy of the whole tensor to the device); ``out``, if given, is a pinned host tensor
-    that receives the (T,B,F) result directly.  Returns (out, sums, loss2_global).  An empty
+    that receives the (T,B,F) result (``staged``: through a device buffer, copied out while the op
+    runs; otherwise written in place by the output pass).  Returns (out, sums, loss2_global).  An empty
     shard is handled as in :func:`sharded_fbw`."""
     num_states, edges, weights, start_end = fsa
     if am_scores_pinned.shape[1] == 0:
@@ -120,6 +121,6 @@ def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None, out=Non
     from .fbw import core
 
     out, sums, loss2 = core.fbw_host_scores(am_scores_pinned, edges, weights, start_end, seq_lens,
-                                            int(num_states), out)
+                                            int(num_states), out, bool(staged))
     reduce_loss(loss2, group)
     return out, sums, loss2

@@ -130,6 +130,17 @@ int fbw_b200_run_for_export(const void* plan, const fbw_b200_summary* summary, c
                             float* out, float* sums, float* loss2, void* work, size_t work_bytes,
                             fbw_b200_stream_t stream);
 
+/* fbw_b200_run for callers whose results live in host memory: same arguments, plus `out_host`, a
+ * PINNED HOST buffer of T*B*F floats that receives a copy of `out` (which stays a device buffer).  The
+ * copy is part of the call: large calls that run as a pipeline over time chunks send every finished
+ * part of the (T,B,F) output to the host (cudaMemcpyAsync on a library-owned stream) while the rest is
+ * still being computed, so the device -> host transfer, which takes longer than the op, starts early;
+ * other calls copy once at the end.  The copy is joined into `stream` before the call returns (the
+ * call still only enqueues).  No counterpart in the reference, whose outputs are device tensors. */
+int fbw_b200_run_host_out(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                          float* out_host, float* sums, float* loss2, void* work, size_t work_bytes,
+                          fbw_b200_stream_t stream);
+
 /* fbw_b200_run with the Python wrapper's elementwise passes folded in (the steps either side of the
  * op in i6_native_ops/fbw/__init__.py:41-44 and :66): the input is log_probs in the caller's own
  * (B,T,F) layout and sign (prepare was given T, B, F of that tensor), the output `grad` (B,T,F) is

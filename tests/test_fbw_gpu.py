@@ -249,12 +249,15 @@ def test_scores_in_pinned_host_memory(fbw_mod, cuda):
         torch.cuda.synchronize()
         assert out_h.is_cuda and torch.equal(sums_h, sums) and torch.equal(out_h, out)
         assert abs(float(loss2[0]) - float(sums.double().sum())) <= 1e-4 * abs(float(sums.double().sum()))
-        # the result written straight into a pinned host tensor by the output pass
-        out_p = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
-        got, sums_p, _ = fbw_mod.fbw_host_scores(am_h, fsa, sl, out=out_p)
-        torch.cuda.synchronize()
-        assert got.data_ptr() == out_p.data_ptr() and torch.equal(sums_p, sums) and torch.equal(out_p, out.cpu())
-        del out_p
+        # the result delivered into a pinned host tensor: copied out piece by piece while the op runs
+        # (staged), or written in place by the output pass
+        for staged in (True, False):
+            out_p = torch.full(am.shape, float("nan"), dtype=am.dtype).pin_memory()
+            got, sums_p, _ = fbw_mod.fbw_host_scores(am_h, fsa, sl, out=out_p, staged=staged)
+            torch.cuda.synchronize()
+            assert got.data_ptr() == out_p.data_ptr() and torch.equal(sums_p, sums)
+            assert torch.equal(out_p, out.cpu())
+            del out_p
         del out, out_h, am
     with pytest.raises(RuntimeError):  # pageable host memory is not addressable from the device
         fbw_mod.core.fbw_host_scores(am_h.clone(), fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
