@@ -9,6 +9,7 @@ large or irregular automata reach:
   * the large-vocabulary CTC batch at full size (B=256, T=400, F=10025);
   * a 64-sequence slice of the full-scale lattice batch (the largest piece of it one call of the
     reference op can take: its 32-bit sizes overflow beyond, i6_native_ops/fbw/fbw_op.cu:268-276);
+  * 24 lattice sequences (the pipeline over time chunks with the large-automaton sweeps);
   * a batch of more than 8192 sequences (grouping by sequence switches to a device-wide sort).
 
 Targets: the fp64 CPU oracle on every sequence (or a sample of eight spread over the cost order) and
@@ -79,6 +80,15 @@ def test_lattice_slice_of_64(fbw_mod, ref_core, cuda):
     b = wl.make_batch("lattice", B=64)
     am = wl.make_scores(b, cuda)
     full_parity("lattice_full_scale B=64", fbw_mod, ref_core, b, am, cuda, sample=8)
+
+
+def test_lattice_time_chunk_pipeline(fbw_mod, ref_core, cuda):
+    """24 full-scale lattice sequences: too few for the size-group schedule, large enough for the
+    pipeline over time chunks, so the sweeps (clusters, state scores stored four frames at a time) run
+    as several launches that hand their state vectors on."""
+    b = wl.make_batch("lattice", B=24)
+    am = wl.make_scores(b, cuda)
+    full_parity("lattice_full_scale B=24 (time chunks)", fbw_mod, ref_core, b, am, cuda, sample=8)
 
 
 def test_more_than_8192_sequences(fbw_mod, cuda):
