@@ -838,6 +838,11 @@ struct RunArgs {
     // 1: the sweeps compute every state's score, also of states that cannot lie on a complete path
     // (the debug export of the forward scores then equals the reference's buffer everywhere)
     int keep_dead_states;
+    // Output in two steps (not null): the sweep launch of a group of sequences also writes the +inf
+    // background of the group's rows of `out` -- one more warp per sweep CTA and `fill_ctas` CTAs that
+    // do nothing else -- and k_patch writes the posteriors into it.  The word counts the rows taken.
+    unsigned long long* next_row;
+    int fill_ctas;
 };
 
 // chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
@@ -922,6 +927,53 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
 }
 
 
+// ---- the output in two steps: background with the sweeps, posteriors afterwards ---------------------
+// Nearly all of the (T,B,F) output is the +inf background, which does not depend on anything the call
+// computes, and the sweeps leave the memory system idle.  So the sweep launch of a group of sequences
+// also writes the background of the group's rows: a warp of its own in every sweep CTA (and a few CTAs
+// that do nothing else, for the SMs without a sweep) hands a constant block of +inf in shared memory
+// to the copy engine over and over (cp.async.bulk shared -> global).  The block never changes, so no
+// store waits for another, and the issue slots stay with the sweep.  Rows are handed out through a
+// counter, so that every SM's copy engine is busy until the group's rows are done.  One warp per row;
+// a row starts at any 4-byte offset: scalar head, 16-byte aligned body in pieces, scalar tail.
+constexpr int kFillFloats = 512;
+
+__device__ __forceinline__ void sweep_sync(int nt) {  // the sweep's threads only (a multiple of 32)
+    asm volatile("bar.sync 1, %0;" ::"r"(nt) : "memory");
+}
+
+__device__ __forceinline__ void background_rows(const RunArgs& a, const float* block) {
+    const int lane = threadIdx.x & 31;
+    const int nb = a.r1 - a.r0;
+    const i64 F = a.F;
+    const i64 rows = a.T * nb;
+    const unsigned src = (unsigned)__cvta_generic_to_shared(block);
+    for (;;) {
+        unsigned long long taken = 0;
+        if (lane == 0) taken = atomicAdd(a.next_row, 1ull);
+        const i64 it = (i64)__shfl_sync(0xffffffffu, taken, 0);
+        if (it >= rows) break;
+        const i64 t = it / nb;
+        const int b = a.order[a.r0 + (int)(it - t * nb)];
+        const i64 rbase = (t * a.B + b) * F;
+        float* __restrict__ row = a.out + rbase;
+        const int head = (int)min((i64)((4 - (rbase & 3)) & 3), F);
+        const i64 body_end = head + (((F - head) >> 2) << 2);
+        if (lane < head) row[lane] = CUDART_INF_F;
+        if (lane < F - body_end) row[body_end + lane] = CUDART_INF_F;
+        for (i64 cs = head + (i64)lane * kFillFloats; cs < body_end; cs += 32 * (i64)kFillFloats) {
+            const unsigned bytes = (unsigned)(min((i64)kFillFloats, body_end - cs) * 4);
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(row + cs), "r"(src),
+                         "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        // a few stores in flight per lane: the next row is taken when the engine has room for it
+        asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the block must outlive the stores
+}
+
 // One persistent CTA per (sequence, direction).  Shared memory holds the sequence's sorted edge list
 // (target-sorted for the forward sweep, source-sorted for the backward one), the state-score
 // vectors and a ring of RING gathered-score rows filled by cp.async a few frames ahead.
@@ -948,7 +1000,23 @@ template <int RING, bool TILED, int KREG, bool PRUNE>
 __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem,
                                                 int nrows) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ __align__(128) float inf_block[kFillFloats];
     const int item = blockIdx.x;
+    const int NT = blockDim.x - (a.next_row != nullptr ? 32 : 0);  // the sweep's threads
+    if (a.next_row != nullptr) {
+        const bool fill_only = item >= 2 * (a.r1 - a.r0);
+        if (fill_only || (int)threadIdx.x >= NT) {
+            // (the threads of a warp that writes the background all come here)
+            for (int i = (fill_only ? threadIdx.x : threadIdx.x - NT); i < kFillFloats;
+                 i += (fill_only ? blockDim.x : 32)) {
+                inf_block[i] = CUDART_INF_F;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (fill_only) __syncthreads(); else __syncwarp();
+            background_rows(a, inf_block);
+            return;
+        }
+    }
     const int b    = a.order[a.r0 + (item >> 1)];  // most expensive sequences first
     const bool fwd = (item & 1) == 0;
     const int  Te  = a.seq_T[b];
@@ -957,7 +1025,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     const int e0 = a.edge_off[b], Eb = a.edge_off[b + 1] - e0;
     const int Db = a.nslot[b];
     const int Dp = (Db + 3) & ~3;
-    const int NT = blockDim.x, tid = threadIdx.x;
+    const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
     // state vectors kept in shared memory: 64 (TILED), else nrows = 2 or 4.  With four, the vectors of
     // four consecutive frames leave as one 16-byte store per state instead of four 4-byte stores.
@@ -989,10 +1057,10 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
         const int far = 0xffff;
         const int origin = fwd ? a.end_l[b] : a.start_l[b];
         for (int s = tid; s < Sb; s += NT) hops[s] = (unsigned short)(s == origin ? 0 : far);
-        __syncthreads();
+        sweep_sync(NT);
         for (int level = 0; level < far - 1; level++) {
             if (tid == 0) settled = 0;
-            __syncthreads();
+            sweep_sync(NT);
             bool any = false;
             for (int s = tid; s < Sb; s += NT) {
                 if (hops[s] == level) {
@@ -1007,9 +1075,9 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
                 }
             }
             if (any) settled = 1;
-            __syncthreads();
+            sweep_sync(NT);
             if (settled == 0) break;  // uniform: read after the barrier, written before it
-            __syncthreads();
+            sweep_sync(NT);
         }
     }
     const int step = fwd ? 1 : -1;
@@ -1030,7 +1098,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             r0[s] = j0 == 0 ? ((s == seed) ? 0.f : CUDART_INF_F) : carry[s];
         }
     }
-    __syncthreads();
+    sweep_sync(NT);
     // frames this launch records, for the tiled flush
     const int f_lo = fwd ? j0 : Te - j1, f_hi = fwd ? j1 - 1 : Te - 1 - j0;
 
@@ -1089,7 +1157,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
     for (int j = j0; j < j1; j++) {
         const int t = t_first + step * j;
         if (RING > 0) cp_async_wait<kWait>();
-        __syncthreads();
+        sweep_sync(NT);
         if (RING > 0) issue(j + RING - 1);
         const float* cur = srow(j, t);
         if (!TILED && kRows == 2) {  // record this frame's state scores (tiled layout: [t/32][state][t%32])
@@ -1289,8 +1357,9 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
 // reference accumulates the same terms with atomics in no fixed order.  A slot with one edge gets
 // x_e - sum exactly.  One CTA per (sequence, 32-frame tile); each warp takes blocks of 32 slots,
 // lane = frame, and writes them out transposed so that every frame's row of P is contiguous.
-__global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
-    __shared__ float stage[4][kTile][kTile + 1];
+constexpr int kClassWarps = 8;  // warps of a k_class CTA: blocks of 32 slots of one unit in flight
+__global__ void __launch_bounds__(32 * kClassWarps) k_class(RunArgs a) {
+    __shared__ float stage[kClassWarps][kTile][kTile + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float (*st)[kTile + 1] = stage[warp];
     const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
@@ -1304,7 +1373,7 @@ __global__ void __launch_bounds__(128, 8) k_class(RunArgs a) {
         const int* __restrict__ mp  = a.m_ptr + p.so;
         float* __restrict__ Pb      = a.P + a.gf_off[p.b];
         const int mbase = mp[0];
-        for (int d0 = warp * kTile; d0 < p.Db; d0 += 4 * kTile) {
+        for (int d0 = warp * kTile; d0 < p.Db; d0 += kClassWarps * kTile) {
             const int nd = min(kTile, p.Db - d0);
             const int j0 = mp[d0] - mbase, j1 = mp[d0 + nd] - mbase;
             int   cur = -1;
@@ -1505,6 +1574,59 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
     __syncwarp();
 }
 
+
+// k_patch, the second step of the output in two steps (the first is background_rows, with the
+// sweeps): the class posteriors go into rows that already hold the +inf background, as whole 32-byte
+// sectors (the posterior and its +inf neighbours), which needs no read of the sector from DRAM; only
+// the sectors that straddle two rows of the output are patched word by word.
+// One warp per output row of a valid frame; lane = class slot.  A slot whose predecessor lies in
+// another 32-byte sector leads its sector: it collects the posteriors of the slots that share the
+// sector (slots are in ascending emission id, so they follow it) and writes the eight words.
+__global__ void __launch_bounds__(256) k_patch(RunArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int B = (int)a.B;
+    const i64 F = a.F;
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    for (i64 idx = blockIdx.x; idx < nunits * 4; idx += gridDim.x) {  // a quarter tile (8 rows) per CTA step
+        const PostUnit p = post_unit(a, u0 + (idx >> 2));
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+        const int t = p.k * kTile + (int)(idx & 3) * 8 + warp;
+        if (t >= p.Te) continue;
+        const int* __restrict__ emis = a.slot_emis + p.so;
+        const float* __restrict__ Pr = a.P + a.gf_off[p.b] + (i64)t * p.Dp;
+        const i64 rbase = ((i64)t * B + p.b) * F;       // first word of the row
+        float* __restrict__ out = a.out;
+        for (int d = lane; d < p.Db; d += 32) {
+            const i64 g  = rbase + emis[d];
+            const i64 sg = g >> 3;                       // 32-byte sector of the output (out is 32-byte aligned)
+            if (d > 0 && ((rbase + emis[d - 1]) >> 3) == sg) continue;  // not the first slot of its sector
+            const i64 s0 = sg << 3;
+            if (s0 >= rbase && s0 + 8 <= rbase + F) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = CUDART_INF_F;
+                for (int k = d; k < p.Db; k++) {
+                    const i64 gk = rbase + emis[k];
+                    if ((gk >> 3) != sg) break;
+                    const int pos = (int)(gk & 7);
+                    const float val = Pr[k];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = (i == pos) ? val : v[i];
+                }
+                float4* dst4 = reinterpret_cast<float4*>(out + s0);
+                dst4[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst4[1] = make_float4(v[4], v[5], v[6], v[7]);
+            } else {  // the sector holds words of a neighbouring row: patch this row's words one by one
+                for (int k = d; k < p.Db; k++) {
+                    const i64 gk = rbase + emis[k];
+                    if ((gk >> 3) != sg) break;
+                    out[gk] = Pr[k];
+                }
+            }
+        }
+    }
+}
+
 // Deterministic reduction of the per-frame sums into two scalars (single block).
 __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i64 T, i64 B,
                                               float* loss2) {
@@ -1530,7 +1652,7 @@ __global__ void __launch_bounds__(1024) k_loss(const float* __restrict__ sums, i
 // host side
 // ---------------------------------------------------------------------------------------------
 struct RunLayout {
-    size_t A, Bt, Gt, Gf, P, X, N, carry, total;
+    size_t A, Bt, Gt, Gf, P, X, N, carry, next_row, total;
 };
 
 RunLayout run_layout(const fbw_b200_summary& s) {
@@ -1549,6 +1671,7 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     L.X     = take((size_t)s.score_floats);
     L.N     = take((size_t)s.post_units * kTile);
     L.carry = take((size_t)(2 * s.S));
+    L.next_row = take(2 * FBW_B200_GROUPS);  // a 64-bit row counter per group (background_rows)
     L.total = off;
     return L;
 }
@@ -1581,6 +1704,8 @@ void plan_args(RunArgs& a, const void* plan, const fbw_b200_summary& s) {
     a.T = s.T; a.B = s.B; a.F = s.F;
     a.r0 = 0; a.r1 = (int)s.B;
     a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
+    a.next_row = nullptr;
+    a.fill_ctas = 0;
 }
 
 // the arguments of one forward-backward call: plan arrays, run scratch, inputs and outputs
@@ -1807,7 +1932,7 @@ SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
     c.dpmax = (int)((md + 3) & ~3);
     c.nt    = (int)((ms + 31) & ~31);
     c.nt    = c.nt < 64 ? 64 : (c.nt > 1024 ? 1024 : c.nt);
-    const size_t limit = 227 * 1024;
+    const size_t limit = 227 * 1024 - sizeof(float) * kFillFloats;  // less the kernel's static block
     auto need = [&](int ring, int rows, int in_smem) {
         const size_t spad = rows == 64 ? (size_t)(c.smax | 1) : (size_t)c.smax;
         return (size_t)4 * ring * c.dpmax + 4 * (((size_t)rows * spad + 3) & ~(size_t)3) +
@@ -1832,9 +1957,38 @@ SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
     return c;
 }
 
+// Whether a call that runs as groups writes its output in two steps (background_rows with the sweeps,
+// k_patch after the posteriors) instead of one pass of k_expand afterwards.  It pays where the rows
+// are sparse (the sectors that hold a posterior are a small part of the row) and the background does
+// not hold up the sweeps: all sweep CTAs resident at once, or a background that takes longer than the
+// sweeps anyway.  Measured, ms per call, one pass against two steps: triphone 64 sequences 2.55 / 2.40,
+// 96 sequences 3.43 / 3.72 (sweep CTAs in two waves: the first wave leaves later), BPE-CTC 256
+// sequences 1.49 / 1.30, 128 sequences 1.06 / 0.90.  FBW_B200_OUTPUT=patch / expand fixes the answer.
+bool output_in_two_steps(const fbw_b200_summary& s, i64 ms, i64 me, i64 md) {
+    static int conf = -1;
+    if (conf < 0) {
+        const char* e = getenv("FBW_B200_OUTPUT");
+        conf = e && strcmp(e, "patch") == 0 ? 1 : (e && strcmp(e, "expand") == 0 ? 0 : 2);
+    }
+    // the sweep CTAs need room for one more warp; automata that large run as clusters anyway
+    if (conf == 0 || s.max_len <= 0 || ms > 992) return false;
+    const SweepShape c = sweep_shape(ms, me, md);
+    if (!c.found) return false;
+    if (conf == 1) return true;
+    if (md * 16 > s.F) return false;  // dense rows: patching would touch most sectors twice
+    const i64 by_smem    = (i64)(227 * 1024) / (i64)(c.smem + sizeof(float) * kFillFloats + 1024);
+    const i64 by_threads = 2048 / (c.nt + 32);
+    const i64 per_sm     = by_smem < by_threads ? (by_smem > 0 ? by_smem : 1) : (by_threads > 0 ? by_threads : 1);
+    const i64 waves      = (2 * s.B + per_sm * sm_count() - 1) / (per_sm * sm_count());
+    if (waves <= 1) return true;
+    const double fill_ms  = (double)s.T * (double)s.B * (double)s.F * 4.0 / 5.0e9;  // at 5 TB/s
+    const double sweep_ms = (double)waves * (double)s.max_len * 0.6e-3;             // 0.6 us per frame
+    return fill_ms >= 1.3 * sweep_ms;
+}
+
 // gather -> sweep -> posterior -> expand for the sequences of ranks [r0, r1) on stream st.
 // ms/me/md: largest state, edge and slot counts in the range (they size the sweep launch).
-enum { kDoGather = 1, kDoSweep = 2, kDoPost = 4, kDoExpand = 8, kDoAll = 15 };
+enum { kDoGather = 1, kDoSweep = 2, kDoPost = 4, kDoExpand = 8, kDoAll = 15, kDoPatch = 16 };
 
 // `what` selects the stages to launch (the time-chunked pipeline launches them on different streams)
 int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b200_summary& s,
@@ -1861,10 +2015,12 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         const int smax = c.smax, dpmax = c.dpmax, nt = c.nt, ring = c.ring, tiled = c.tiled;
         const int in_smem = c.in_smem;
         const size_t smem = c.smem;
-        const int grid = 2 * nb;
+        // with the background: a warp more per CTA, and CTAs that do nothing else
+        const int grid = 2 * nb + (a.next_row != nullptr ? a.fill_ctas : 0);
+        const int nthreads = nt + (a.next_row != nullptr ? 32 : 0);
         int rc;
 #define SWEEP_CASE(R, TL) \
-    rc = launch_sweep<R, TL>(a, grid, nt, smem, smax, dpmax, in_smem, c.rows, (int)s.max_degree, st)
+    rc = launch_sweep<R, TL>(a, grid, nthreads, smem, smax, dpmax, in_smem, c.rows, (int)s.max_degree, st)
         if (tiled) {
             switch (ring) {
                 case 16: SWEEP_CASE(16, true); break;
@@ -1891,13 +2047,19 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         int g1 = (int)(units < (i64)sms * 8 ? units : (i64)sms * 8);
         i64 w2 = (units + 3) / 4;
         int g2 = (int)(w2 < (i64)sms * 16 ? w2 : (i64)sms * 16);
-        int g3 = (int)(units < (i64)sms * 12 ? units : (i64)sms * 12);
+        int g3 = (int)(units < (i64)sms * 6 ? units : (i64)sms * 6);
         k_score<<<g1 > 0 ? g1 : 1, 256, 0, st>>>(a);
         k_norm<<<g2 > 0 ? g2 : 1, 128, 0, st>>>(a);
-        k_class<<<g3 > 0 ? g3 : 1, 128, 0, st>>>(a);
+        k_class<<<g3 > 0 ? g3 : 1, 32 * kClassWarps, 0, st>>>(a);
         COUNT_LAUNCH(3);
     }
     if (ev) CUDA_OK(cudaEventRecord(ev[3], st));
+    if (what & kDoPatch) {
+        const i64 want = tiles * nb * 4;
+        int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
+        k_patch<<<grid > 0 ? grid : 1, 256, 0, st>>>(a);
+        COUNT_LAUNCH(1);
+    }
     if (what & kDoExpand) {
         i64 want = ((s.T + kTile - 1) / kTile) * nb * 4;
         int grid = (int)(want < (i64)sms * 8 ? want : (i64)sms * 8);
@@ -2163,6 +2325,9 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     i64 ms, me, md;
     plan_maxima(s, ms, me, md);
+    const bool two_step = G > 1 && !fused && !a.out_plain && (((uintptr_t)out & 31) == 0) &&
+                          output_in_two_steps(s, ms, me, md);
+    if (two_step && G == 8 && !getenv("FBW_B200_NUM_GROUPS")) G = 4;
     // every launch shape is checked before anything is enqueued, so that a call that cannot run
     // fails before it has forked onto the auxiliary streams
     if (s.max_len > 0) {
@@ -2174,7 +2339,6 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     int rc_forked = FBW_B200_OK;
     if (G > 1 && pool) {
         std::unique_lock<std::mutex> lock(pool->mu);
-        CUDA_OK(cudaEventRecord(pool->fork, st));
         const int per = FBW_B200_GROUPS / G;  // base groups merged into one launch group
         // the cheapest group goes first: its sweeps end first and its output stages start while the
         // expensive groups are still sweeping (FBW_B200_GROUP_ORDER=0: most expensive first)
@@ -2208,26 +2372,47 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             }
         }
         // with clusters the long sequences are the critical path: they start first
-        const bool cheapest_first = reverse && !clustered;
+        const bool cheapest_first = reverse && !clustered && !two_step;
+        struct GroupRun { int r0, r1, cs; i64 ms, me, md; cudaStream_t st; } runs[FBW_B200_GROUPS];
+        int nruns = 0;
         for (int gi = 0; gi < G; gi++) {
             const int g = cheapest_first ? G - 1 - gi : gi;
-            const int r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
-            const int r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
-            if (r1 <= r0) continue;
-            i64 gs_ = 0, ge_ = 0, gd_ = 0;
+            GroupRun r;
+            r.r0 = (int)(((i64)(g * per) * s.B) / FBW_B200_GROUPS);
+            r.r1 = (int)(((i64)((g + 1) * per) * s.B) / FBW_B200_GROUPS);
+            if (r.r1 <= r.r0) continue;
+            r.ms = r.me = r.md = 0;
             for (int q = g * per; q < (g + 1) * per; q++) {
-                gs_ = s.group_max_states[q] > gs_ ? s.group_max_states[q] : gs_;
-                ge_ = s.group_max_edges[q] > ge_ ? s.group_max_edges[q] : ge_;
-                gd_ = s.group_max_slots[q] > gd_ ? s.group_max_slots[q] : gd_;
+                r.ms = s.group_max_states[q] > r.ms ? s.group_max_states[q] : r.ms;
+                r.me = s.group_max_edges[q] > r.me ? s.group_max_edges[q] : r.me;
+                r.md = s.group_max_slots[q] > r.md ? s.group_max_slots[q] : r.md;
             }
-            cudaStream_t gstream = gi == 0 ? st : pool->aux[gi];
-            if (gi > 0 && cudaStreamWaitEvent(gstream, pool->fork, 0) != cudaSuccess) {
+            r.cs = group_cs[g];
+            r.st = nruns == 0 ? st : pool->aux[nruns];
+            runs[nruns++] = r;
+        }
+        unsigned long long* next_row = reinterpret_cast<unsigned long long*>(at<float>(work, R.next_row));
+        if (two_step && cudaMemsetAsync(next_row, 0, sizeof(*next_row) * FBW_B200_GROUPS, st) != cudaSuccess) {
+            return FBW_B200_CUDA_ERROR;
+        }
+        CUDA_OK(cudaEventRecord(pool->fork, st));
+        // with the output in two steps the SMs without a sweep CTA get CTAs that only write background
+        const int idle_sms = sm_count() - 2 * (int)s.B;
+        for (int i = 0; i < nruns; i++) {
+            const GroupRun& r = runs[i];
+            if (i > 0 && cudaStreamWaitEvent(r.st, pool->fork, 0) != cudaSuccess) {
                 rc_forked = FBW_B200_CUDA_ERROR;
                 break;
             }
-            int rc = launch_group(a, r0, r1, gs_, ge_, gd_, s, gstream, nullptr, kDoAll, group_cs[g]);
-            if (gi > 0 && (cudaEventRecord(pool->join[gi], gstream) != cudaSuccess ||
-                           cudaStreamWaitEvent(st, pool->join[gi], 0) != cudaSuccess)) {
+            RunArgs ag = a;
+            if (two_step) {
+                ag.next_row  = next_row + i;
+                ag.fill_ctas = idle_sms > 0 ? (idle_sms + i) / nruns : 0;
+            }
+            int rc = launch_group(ag, r.r0, r.r1, r.ms, r.me, r.md, s, r.st, nullptr,
+                                  two_step ? (kDoGather | kDoSweep | kDoPost | kDoPatch) : kDoAll, r.cs);
+            if (i > 0 && (cudaEventRecord(pool->join[i], r.st) != cudaSuccess ||
+                          cudaStreamWaitEvent(st, pool->join[i], 0) != cudaSuccess)) {
                 rc = rc != FBW_B200_OK ? rc : FBW_B200_CUDA_ERROR;
             }
             if (rc != FBW_B200_OK) {
