@@ -1280,12 +1280,9 @@ __device__ __forceinline__ PostUnit post_unit(const RunArgs& a, i64 u) {
 // has score +inf and so has the sum, which is what the reference stores for such an edge
 // (fbw_op.cu:82-85).  One CTA per (sequence, 32-frame tile), lane = frame; in the tiled layouts
 // every load and store of a warp is one 128-byte line.  Fully parallel: no fold here.
-__global__ void __launch_bounds__(256) k_score(RunArgs a) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
-    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
-        const PostUnit p = post_unit(a, u0 + idx);
-        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+// (the work of `nwarps` warps on one unit; `warp` is this warp's number among them)
+__device__ __forceinline__ void score_unit(const RunArgs& a, const PostUnit& p, int lane, int warp, int nwarps) {
+    {
         const bool valid = p.k * kTile + lane < p.Te;
         // every lane loads (a tile is allocated for all 32 frames); frames past the sequence's
         // length hold unspecified values and get +inf
@@ -1294,7 +1291,7 @@ __global__ void __launch_bounds__(256) k_score(RunArgs a) {
         const float* __restrict__ Gb = a.Gt + a.tg_off[p.b] + (i64)p.k * p.Db * kTile + lane;
         float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
         const int4* __restrict__ q = a.q_rec + p.e0;
-        for (int i0 = warp * kPostBatch; i0 < p.Eb; i0 += 8 * kPostBatch) {
+        for (int i0 = warp * kPostBatch; i0 < p.Eb; i0 += nwarps * kPostBatch) {
             int4  r[kPostBatch];
             float al[kPostBatch], be[kPostBatch], g[kPostBatch];
 #pragma unroll
@@ -1314,19 +1311,25 @@ __global__ void __launch_bounds__(256) k_score(RunArgs a) {
     }
 }
 
+__global__ void __launch_bounds__(256) k_score(RunArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+        score_unit(a, p, lane, warp, 8);
+    }
+}
+
 // Frame normalisers: sum = left fold of prob_add over the sequence's edges in ascending edge index
 // (fbw_op.cu:115-118), sums[t,b] = isinf(sum) ? 0 : sum (fbw_op.cu:120-129).  One warp per
 // (sequence, 32-frame tile), lane = frame, streaming the tile's edge scores in storage order; the
 // next 8 lines are loaded while the current 8 are folded.  Steps whose result is provably the
 // running minimum skip expf/log1pf (exact).  The raw sum (+inf for a dead frame) goes to N.
 // Every unit is its own warp so that all the serial folds of a call run side by side.
-__global__ void __launch_bounds__(128) k_norm(RunArgs a) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
-    const i64 W = (i64)gridDim.x * 4;
-    for (i64 idx = (i64)blockIdx.x * 4 + warp; idx < nunits; idx += W) {
-        const PostUnit p = post_unit(a, u0 + idx);
-        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+// (one warp folds one unit; returns the raw sum of the lane's frame)
+__device__ __forceinline__ float norm_unit(const RunArgs& a, const PostUnit& p, int lane) {
+    {
         const int  t     = p.k * kTile + lane;
         const bool valid = t < p.Te;
         const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
@@ -1348,6 +1351,18 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
         }
         if (valid) a.sums[(i64)t * a.B + p.b] = isinf(acc) ? 0.f : acc;
         a.N[p.u * kTile + lane] = acc;
+        return acc;
+    }
+}
+
+__global__ void __launch_bounds__(128) k_norm(RunArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    const i64 W = (i64)gridDim.x * 4;
+    for (i64 idx = (i64)blockIdx.x * 4 + warp; idx < nunits; idx += W) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+        norm_unit(a, p, lane);
     }
 }
 
@@ -1357,23 +1372,18 @@ __global__ void __launch_bounds__(128) k_norm(RunArgs a) {
 // reference accumulates the same terms with atomics in no fixed order.  A slot with one edge gets
 // x_e - sum exactly.  One CTA per (sequence, 32-frame tile); each warp takes blocks of 32 slots,
 // lane = frame, and writes them out transposed so that every frame's row of P is contiguous.
-constexpr int kClassWarps = 8;  // warps of a k_class CTA: blocks of 32 slots of one unit in flight
-__global__ void __launch_bounds__(32 * kClassWarps) k_class(RunArgs a) {
-    __shared__ float stage[kClassWarps][kTile][kTile + 1];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float (*st)[kTile + 1] = stage[warp];
-    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
-    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
-        const PostUnit p = post_unit(a, u0 + idx);
-        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
-        const float acc = a.N[p.u * kTile + lane];
+// (the work of `nwarps` warps on one unit; `st` is this warp's 32 x 33 staging tile, `acc` the raw
+// sum of the lane's frame)
+__device__ __forceinline__ void class_unit(const RunArgs& a, const PostUnit& p, int lane, int warp, int nwarps,
+                                           float (*st)[kTile + 1], float acc) {
+    {
         const bool rowdead = !(acc < CUDART_INF_F);  // no path through this frame
         const float* __restrict__ Xb = a.X + a.tx_off[p.b] + (i64)p.k * p.Eb * kTile + lane;
         const int2* __restrict__ m  = a.m_pos + p.e0;
         const int* __restrict__ mp  = a.m_ptr + p.so;
         float* __restrict__ Pb      = a.P + a.gf_off[p.b];
         const int mbase = mp[0];
-        for (int d0 = warp * kTile; d0 < p.Db; d0 += kClassWarps * kTile) {
+        for (int d0 = warp * kTile; d0 < p.Db; d0 += nwarps * kTile) {
             const int nd = min(kTile, p.Db - d0);
             const int j0 = mp[d0] - mbase, j1 = mp[d0 + nd] - mbase;
             int   cur = -1;
@@ -1419,6 +1429,18 @@ __global__ void __launch_bounds__(32 * kClassWarps) k_class(RunArgs a) {
             }
             __syncwarp();
         }
+    }
+}
+
+constexpr int kClassWarps = 8;  // warps of a k_class CTA: blocks of 32 slots of one unit in flight
+__global__ void __launch_bounds__(32 * kClassWarps) k_class(RunArgs a) {
+    __shared__ float stage[kClassWarps][kTile][kTile + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
+    for (i64 idx = blockIdx.x; idx < nunits; idx += gridDim.x) {
+        const PostUnit p = post_unit(a, u0 + idx);
+        if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
+        class_unit(a, p, lane, warp, kClassWarps, stage[warp], a.N[p.u * kTile + lane]);
     }
 }
 
@@ -1582,48 +1604,50 @@ __global__ void __launch_bounds__(256) k_expand(RunArgs a) {
 // One warp per output row of a valid frame; lane = class slot.  A slot whose predecessor lies in
 // another 32-byte sector leads its sector: it collects the posteriors of the slots that share the
 // sector (slots are in ascending emission id, so they follow it) and writes the eight words.
+__device__ __forceinline__ void patch_row(const RunArgs& a, const PostUnit& p, int t, int lane) {
+    const int* __restrict__ emis = a.slot_emis + p.so;
+    const float* __restrict__ Pr = a.P + a.gf_off[p.b] + (i64)t * p.Dp;
+    const i64 F     = a.F;
+    const i64 rbase = ((i64)t * a.B + p.b) * F;  // first word of the row
+    float* __restrict__ out = a.out;
+    for (int d = lane; d < p.Db; d += 32) {
+        const i64 g  = rbase + emis[d];
+        const i64 sg = g >> 3;  // 32-byte sector of the output (out is 32-byte aligned)
+        if (d > 0 && ((rbase + emis[d - 1]) >> 3) == sg) continue;  // not the first slot of its sector
+        const i64 s0 = sg << 3;
+        if (s0 >= rbase && s0 + 8 <= rbase + F) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = CUDART_INF_F;
+            for (int k = d; k < p.Db; k++) {
+                const i64 gk = rbase + emis[k];
+                if ((gk >> 3) != sg) break;
+                const int pos = (int)(gk & 7);
+                const float val = Pr[k];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = (i == pos) ? val : v[i];
+            }
+            float4* dst4 = reinterpret_cast<float4*>(out + s0);
+            dst4[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst4[1] = make_float4(v[4], v[5], v[6], v[7]);
+        } else {  // the sector holds words of a neighbouring row: patch this row's words one by one
+            for (int k = d; k < p.Db; k++) {
+                const i64 gk = rbase + emis[k];
+                if ((gk >> 3) != sg) break;
+                out[gk] = Pr[k];
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) k_patch(RunArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int B = (int)a.B;
-    const i64 F = a.F;
     const i64 u0 = a.pu_off[a.r0], nunits = a.pu_off[a.r1] - u0;
     for (i64 idx = blockIdx.x; idx < nunits * 4; idx += gridDim.x) {  // a quarter tile (8 rows) per CTA step
         const PostUnit p = post_unit(a, u0 + (idx >> 2));
         if (!in_chunks(tile_done_chunk(p.k, p.Te, a.chunk_steps), a)) continue;
         const int t = p.k * kTile + (int)(idx & 3) * 8 + warp;
-        if (t >= p.Te) continue;
-        const int* __restrict__ emis = a.slot_emis + p.so;
-        const float* __restrict__ Pr = a.P + a.gf_off[p.b] + (i64)t * p.Dp;
-        const i64 rbase = ((i64)t * B + p.b) * F;       // first word of the row
-        float* __restrict__ out = a.out;
-        for (int d = lane; d < p.Db; d += 32) {
-            const i64 g  = rbase + emis[d];
-            const i64 sg = g >> 3;                       // 32-byte sector of the output (out is 32-byte aligned)
-            if (d > 0 && ((rbase + emis[d - 1]) >> 3) == sg) continue;  // not the first slot of its sector
-            const i64 s0 = sg << 3;
-            if (s0 >= rbase && s0 + 8 <= rbase + F) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) v[i] = CUDART_INF_F;
-                for (int k = d; k < p.Db; k++) {
-                    const i64 gk = rbase + emis[k];
-                    if ((gk >> 3) != sg) break;
-                    const int pos = (int)(gk & 7);
-                    const float val = Pr[k];
-#pragma unroll
-                    for (int i = 0; i < 8; i++) v[i] = (i == pos) ? val : v[i];
-                }
-                float4* dst4 = reinterpret_cast<float4*>(out + s0);
-                dst4[0] = make_float4(v[0], v[1], v[2], v[3]);
-                dst4[1] = make_float4(v[4], v[5], v[6], v[7]);
-            } else {  // the sector holds words of a neighbouring row: patch this row's words one by one
-                for (int k = d; k < p.Db; k++) {
-                    const i64 gk = rbase + emis[k];
-                    if ((gk >> 3) != sg) break;
-                    out[gk] = Pr[k];
-                }
-            }
-        }
+        if (t < p.Te) patch_row(a, p, t, lane);
     }
 }
 
