@@ -54,7 +54,7 @@ CPU_SAMPLE_SEQS = None  # None: the full per-GPU batch of the workload
 
 # dram__bytes_read.sum + dram__bytes_write.sum over all kernels of ONE op call, from an ncu capture
 # of exactly that workload and per-GPU batch size; other sizes report no traffic figure.
-MEASURED_TRAFFIC = {("triphone", 64): 7.699e9}  # (workload, sequences per GPU) -> bytes per call
+MEASURED_TRAFFIC = {("triphone", 64): 9.106e9}  # (workload, sequences per GPU) -> bytes per call
 
 
 def peaks():
