@@ -676,8 +676,9 @@ def main():
 
         def step_host_to_host():
             # scores read in place from pinned host memory by the gather (no copy of the tensor to the
-            # device); the (T,B,F) result is produced on the device and its finished parts are copied
-            # to pinned host memory while the op is still running
+            # device); of the (T,B,F) result only the class posteriors cross the bus, and the library's
+            # host threads write the rows into pinned host memory while the device goes on (rows that
+            # are not sparse would be produced on the device and copied out piece by piece instead)
             e_, w_, se_, sl_ = [t.to(dev, non_blocking=True) for t in host_fsa]
             _, sums, loss2 = sharding.sharded_fbw_host_scores(am_h, (fsa[0], e_, w_, se_), sl_, out=out_h)
             return finish(sums, loss2)
@@ -723,10 +724,20 @@ def main():
                     "rank_bus_gbs": [(h2d + d2h) / (m * 1e-3) / 1e9 for m in rank_ms]}
 
         sectors = batch.score_sector_bytes()
-        e2e = time_leg(step_host_to_host, sectors + fsa_bytes, out_bytes + small_d2h,
+        info = core.fbw_prepare(fsa[1], fsa[2], fsa[3], seq_lens, batch.T, batch.F, int(fsa[0])).info()
+        sparse_rows = info["max_slots"] * 16 <= batch.F
+        # what crosses the bus for the result: the posteriors and five small plan arrays where the host
+        # writes the rows, else the whole tensor
+        posterior_bytes = info["frame_floats"] * 4 + 20 * batch.B + 4 * (batch.num_edges + batch.B + 1)
+        e2e = time_leg(step_host_to_host, sectors + fsa_bytes,
+                       (posterior_bytes if sparse_rows else out_bytes) + small_d2h,
                        "inputs and results in pinned host memory: scores read in place by the op's gather "
-                       f"(32-byte sectors of a {am_h.numel() * 4}-byte tensor), the (T,B,F) result copied "
-                       "device -> host piece by piece while the op runs, sums and loss copied back")
+                       f"(32-byte sectors of a {am_h.numel() * 4}-byte tensor); the (T,B,F) result of {out_bytes} bytes "
+                       + ("is written into pinned host memory by the library's host threads from the class posteriors, "
+                          "which are all of it that crosses the bus (d2h_bytes_per_step), while the device goes on"
+                          if sparse_rows else "is copied device -> host piece by piece while the op runs")
+                       + "; sums and loss copied back")
+        e2e["result_bytes_per_step"] = int(out_bytes)
         e2e_in_place = time_leg(step_in_place, sectors + fsa_bytes, out_bytes + small_d2h,
                                 "as e2e, but the op's output pass writes the (T,B,F) result straight into "
                                 "pinned host memory (no device copy of the result)")

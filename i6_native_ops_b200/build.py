@@ -40,12 +40,15 @@ def _newer(target: str, sources) -> bool:
 def build_lib(force: bool = False, verbose: bool = False) -> str:
     src = os.path.join(PKG, "csrc", "fbw_b200.cu")
     csrc = os.path.join(PKG, "csrc")
-    deps = [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cu", ".inc"))]  # the .inc files are included by fbw_b200.cu
+    # the .inc files are included by fbw_b200.cu; host_fill.cpp is the library's one host-only source
+    host_src = os.path.join(csrc, "host_fill.cpp")
+    deps = [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cu", ".inc"))]
+    deps += [host_src, os.path.join(csrc, "host_fill.h")]
     hdr = os.path.join(INCLUDE, "fbw_b200.h")
     if not force and _newer(LIB, deps + [hdr]):
         return LIB
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB, src]
+    cmd = [nvcc, *NVCC_FLAGS, "-Xcompiler", "-pthread", "-I", INCLUDE, "-o", LIB, src, host_src]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd))

@@ -29,6 +29,8 @@
 //     (fbw_op.cu:115-118); state and class accumulations also run in ascending edge index (the
 //     reference's atomics have no defined order; with at most two terms the order is immaterial).
 
+#include "host_fill.h"
+#include <limits>
 #include "fbw_b200.h"
 
 #include <cuda_runtime.h>
@@ -1700,6 +1702,29 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     return L;
 }
 
+// pinned host scratch of fbw_b200_run_to_host: the plan arrays the host threads read and the posteriors
+struct HostLayout {
+    size_t seq_T, nslot, slot_off, gf_off, slot_emis, P, total;
+};
+
+HostLayout host_layout(const fbw_b200_summary& s) {
+    HostLayout H;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    H.seq_T     = take(4 * (size_t)s.B);
+    H.nslot     = take(4 * (size_t)s.B);
+    H.slot_off  = take(4 * (size_t)s.B);
+    H.gf_off    = take(8 * (size_t)s.B);
+    H.slot_emis = take(4 * (size_t)(s.E + s.B + 1));  // the plan's array: a sequence's classes start at slot_off[b] <= E
+    H.P         = take(4 * ((size_t)s.frame_floats + 8));
+    H.total     = off;
+    return H;
+}
+
 // the plan's arrays as kernel arguments: every sequence, one time chunk covering all frames
 void plan_args(RunArgs& a, const void* plan, const fbw_b200_summary& s) {
     const PlanLayout L = plan_layout(s.B, s.E, s.S);
@@ -1865,6 +1890,9 @@ struct StreamPool {
     cudaStream_t aux[FBW_B200_GROUPS];
     cudaStream_t copy;  // device -> host copies of finished parts of the output
     cudaEvent_t  fork, join[FBW_B200_GROUPS], copied;
+    // fbw_b200_run_to_host: one such call per device at a time (its thread waits on these events)
+    std::mutex   host_mu;
+    cudaEvent_t  host_ready, host_done[kMaxChunks];
     cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks], expanded[kMaxChunks];
 };
 StreamPool g_pools[kMaxDevices];
@@ -1884,8 +1912,10 @@ StreamPool* stream_pool() {
             ok = cudaStreamCreateWithFlags(&p->aux[i], cudaStreamNonBlocking) == cudaSuccess &&
                  cudaEventCreateWithFlags(&p->join[i], cudaEventDisableTiming) == cudaSuccess;
         }
+        ok = ok && cudaEventCreateWithFlags(&p->host_ready, cudaEventDisableTiming) == cudaSuccess;
         for (int i = 0; i < kMaxChunks && ok; i++) {
-            ok = cudaEventCreateWithFlags(&p->gathered[i], cudaEventDisableTiming) == cudaSuccess &&
+            ok = cudaEventCreateWithFlags(&p->host_done[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&p->gathered[i], cudaEventDisableTiming) == cudaSuccess &&
                  cudaEventCreateWithFlags(&p->swept[i], cudaEventDisableTiming) == cudaSuccess &&
                  cudaEventCreateWithFlags(&p->expanded[i], cudaEventDisableTiming) == cudaSuccess;
         }
@@ -2097,7 +2127,7 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
 
 extern "C" {
 
-int fbw_b200_abi_version(void) { return 3; }
+int fbw_b200_abi_version(void) { return 4; }
 
 const char* fbw_b200_status_string(int status) {
     switch (status) {
@@ -2302,7 +2332,11 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
                     fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0,
-                    float* out_host = nullptr) {
+                    float* out_host = nullptr, void* host_work = nullptr) {
+    // host_work (fbw_b200_run_to_host, sparse rows): `out` IS the pinned host buffer.  No kernel
+    // composes rows: the class posteriors go to pinned host memory (in host_work) as the posterior
+    // stages finish, and host threads write the rows from them (host_fill.cpp) while the device goes on.
+    const bool host_patch = host_work != nullptr;
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -2312,6 +2346,42 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     RunArgs a = fbw_args(plan, s, work, R, am, out, sums, loss2, fused);
     a.keep_dead_states = keep_dead_states;
+    fbw_b200::HostRows host_rows;
+    const HostLayout H = host_layout(s);
+    StreamPool* host_pool = host_patch ? stream_pool() : nullptr;
+    std::unique_lock<std::mutex> host_lock;
+    int  host_first_chunk = 0, host_chunks = 0;
+    if (host_patch) {
+        if (fused || out_host) return FBW_B200_BAD_ARGUMENT;
+        if (!host_pool) return FBW_B200_CUDA_ERROR;
+        host_lock = std::unique_lock<std::mutex>(host_pool->host_mu);
+        // the little the host has to know about the plan, and the posteriors' place in host memory
+        const PlanLayout L = plan_layout(s.B, s.E, s.S);
+        char* hw = static_cast<char*>(host_work);
+        CUDA_OK(cudaMemcpyAsync(hw + H.seq_T, at<int>(plan, L.seq_T), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+        CUDA_OK(cudaMemcpyAsync(hw + H.nslot, at<int>(plan, L.nslot), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+        CUDA_OK(cudaMemcpyAsync(hw + H.slot_off, at<int>(plan, L.slot_off), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+        CUDA_OK(cudaMemcpyAsync(hw + H.gf_off, at<i64>(plan, L.gf_off), 8 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+        CUDA_OK(cudaMemcpyAsync(hw + H.slot_emis, at<int>(plan, L.slot_emis), 4 * (size_t)(s.E + s.B + 1),
+                                cudaMemcpyDeviceToHost, st));
+        CUDA_OK(cudaEventRecord(host_pool->host_ready, st));
+        a.P = reinterpret_cast<float*>(hw + H.P);
+        host_rows.T = s.T; host_rows.B = s.B; host_rows.F = s.F;
+        host_rows.seq_T     = reinterpret_cast<const int*>(hw + H.seq_T);
+        host_rows.nslot     = reinterpret_cast<const int*>(hw + H.nslot);
+        host_rows.slot_off  = reinterpret_cast<const int*>(hw + H.slot_off);
+        host_rows.gf_off    = reinterpret_cast<const int64_t*>(hw + H.gf_off);
+        host_rows.slot_emis = reinterpret_cast<const int*>(hw + H.slot_emis);
+        host_rows.P   = a.P;
+        host_rows.out = out;
+        host_rows.chunk_steps = 1 << 30;
+        host_rows.first_chunk = 0;
+        host_rows.num_slots = s.E + s.B + 1;
+        host_rows.p_floats  = s.frame_floats;
+    }
+    const int host_nthreads = host_patch ? fbw_b200::host_threads() : 0;
+    // the stages every schedule below runs for a group of sequences or a time chunk
+    const int kStages = host_patch ? (kDoGather | kDoSweep | kDoPost) : kDoAll;
 
     // frames at or past seq_len keep sums = 0 (fbw_op.cu:120-124)
     CUDA_OK(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)(s.T * s.B), st));
@@ -2343,9 +2413,11 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         } else {
             (void)cudaGetLastError();
         }
+        if (host_patch && !a.out_plain) return FBW_B200_BAD_ARGUMENT;
     }
     int G = ev ? 1 : choose_groups(s);
     if (G > 1 && host_scores && !(s.max_edges >= 2048 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E)) G = 1;
+    if (host_patch) G = 1;  // the host's row order follows the time chunks
     const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     i64 ms, me, md;
     plan_maxima(s, ms, me, md);
@@ -2434,7 +2506,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
                 ag.fill_ctas = idle_sms > 0 ? (idle_sms + i) / nruns : 0;
             }
             int rc = launch_group(ag, r.r0, r.r1, r.ms, r.me, r.md, s, r.st, nullptr,
-                                  two_step ? (kDoGather | kDoSweep | kDoPost | kDoPatch) : kDoAll, r.cs);
+                                  two_step ? (kDoGather | kDoSweep | kDoPost | kDoPatch) : kStages, r.cs);
             if (i > 0 && (cudaEventRecord(pool->join[i], r.st) != cudaSuccess ||
                           cudaStreamWaitEvent(st, pool->join[i], 0) != cudaSuccess)) {
                 rc = rc != FBW_B200_OK ? rc : FBW_B200_CUDA_ERROR;
@@ -2488,8 +2560,11 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         for (int c = 0; c < C && go; c++) {
             if (!(c == 0 || c >= first_finish)) continue;
             cudaStream_t ps = pool->aux[1 + c % kPostStreams];
-            go = ok(cudaStreamWaitEvent(ps, pool->swept[c], 0)) &&
-                 stage(c, ps, c >= first_finish ? (kDoPost | kDoExpand) : kDoExpand);
+            go = ok(cudaStreamWaitEvent(ps, pool->swept[c], 0));
+            // (tiles past a sequence's end go with chunk 0: nothing to do for them in host_patch mode)
+            if (c >= first_finish) go = go && stage(c, ps, host_patch ? kDoPost : (kDoPost | kDoExpand));
+            else if (!host_patch) go = go && stage(c, ps, kDoExpand);
+            if (host_patch && c >= first_finish) go = go && ok(cudaEventRecord(host_pool->host_done[c], ps));
             if (go && out_host) {
                 // The frames of a 32-frame tile are complete for EVERY sequence once the output
                 // stages of the chunk in which the longest sequence finishes that tile have run (a
@@ -2528,6 +2603,10 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             }
             out_host = nullptr;  // done piecewise
         }
+        host_first_chunk = first_finish;
+        host_chunks = C;
+        host_rows.chunk_steps = a.chunk_steps;
+        host_rows.first_chunk = first_finish;
         // join: the gather stream and the output streams back into the caller's stream
         for (int i = 0; i <= kPostStreams; i++) {
             if (cudaEventRecord(pool->join[i], pool->aux[i]) != cudaSuccess ||
@@ -2537,11 +2616,27 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         }
     } else {
         int spare = sm_count() - 2 * (int)s.B;
-        int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kDoAll,
+        int rc = launch_group(a, 0, (int)s.B, ms, me, md, s, st, ev, kStages,
                               sweep_cluster_size(ms, 2 * (int)s.B, &spare));
         if (rc != FBW_B200_OK) return rc;
     }
     if (rc_forked != FBW_B200_OK) return rc_forked;
+    if (host_patch) {
+        // The device work is enqueued; this thread now writes the rows.  Those past the sequences'
+        // ends need no posteriors; the others follow chunk by chunk as the posterior stages finish
+        // (a call without time chunks has one chunk, complete when everything on `st` so far is).
+        if (host_chunks == 0) {
+            CUDA_OK(cudaEventRecord(host_pool->host_done[0], st));
+            host_chunks = 1;
+        }
+        CUDA_OK(cudaEventSynchronize(host_pool->host_ready));
+        bool rows_ok = fbw_b200::host_compose(host_rows, -1, host_nthreads);
+        for (int c = host_first_chunk; c < host_chunks; c++) {
+            CUDA_OK(cudaEventSynchronize(host_pool->host_done[c]));
+            rows_ok = fbw_b200::host_compose(host_rows, c, host_nthreads) && rows_ok;
+        }
+        if (!rows_ok) return FBW_B200_BAD_ARGUMENT;
+    }
     if (out_host) {  // schedules without time chunks: one copy behind everything
         CUDA_OK(cudaMemcpyAsync(out_host, out, (size_t)s.T * s.B * s.F * sizeof(float), cudaMemcpyDeviceToHost, st));
     }
@@ -2578,6 +2673,33 @@ int fbw_b200_run_host_out(const void* plan, const fbw_b200_summary* summary, con
                           fbw_b200_stream_t stream) {
     if (!out_host) return FBW_B200_BAD_ARGUMENT;
     return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, out_host);
+}
+
+size_t fbw_b200_run_to_host_bytes(const fbw_b200_summary* summary) {
+    if (!summary) return 0;
+    return host_layout(*summary).total;
+}
+
+int fbw_b200_run_to_host(const void* plan, const fbw_b200_summary* summary, const float* am, float* out_host,
+                         float* sums, float* loss2, void* work, size_t work_bytes, void* host_work,
+                         size_t host_work_bytes, fbw_b200_stream_t stream) {
+    if (!summary || !out_host) return FBW_B200_BAD_ARGUMENT;
+    i64 ms, me, md;
+    plan_maxima(*summary, ms, me, md);
+    static int conf = -1;  // FBW_B200_HOST_ROWS=0: always let the device's output pass write the rows
+    if (conf < 0) { const char* e = getenv("FBW_B200_HOST_ROWS"); conf = e ? atoi(e) : 1; }
+    const bool sparse = conf && md * 16 <= summary->F && ((uintptr_t)out_host & 3) == 0;
+    if (sparse) {
+        if (!host_work || ((uintptr_t)host_work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
+        if (host_work_bytes < host_layout(*summary).total) return FBW_B200_WORKSPACE;
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, host_work) != cudaSuccess || attr.type != cudaMemoryTypeHost) {
+            (void)cudaGetLastError();
+            return FBW_B200_BAD_ARGUMENT;  // has to be pinned: the device writes the posteriors there
+        }
+    }
+    return run_impl(plan, summary, am, out_host, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, nullptr,
+                    sparse ? host_work : nullptr);
 }
 
 int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,

@@ -182,15 +182,17 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
     auto dev_opts = weights.options();  // float32 on the automata's device
     torch::Tensor out, out_dev;
     if (out_pinned.has_value()) {
-        // The (T,B,F) result ends up in the caller's pinned host tensor.  staged: it is produced in
-        // a device buffer and copied out piece by piece while the rest is still being computed (the
-        // copy engine is the faster way over the bus); otherwise the output pass writes it straight
-        // into host memory and no device copy of it exists.
+        // The (T,B,F) result ends up in the caller's pinned host tensor.  staged: the library picks the
+        // faster way over the bus -- where the rows are sparse, only the class posteriors are sent and
+        // host threads write the rows from them while the device goes on (fbw_b200_run_to_host; the
+        // call then returns when the rows are written); else the result is produced in a device buffer
+        // and copied out piece by piece while the rest is still being computed.  Not staged: the
+        // output pass writes every row straight into host memory.  No device copy of the result is
+        // kept in either case.
         out = *out_pinned;
         TORCH_CHECK(!out.is_cuda() && out.is_pinned() && out.is_contiguous() &&
                         out.scalar_type() == torch::kFloat32 && out.sizes() == am_scores.sizes(),
                     "out must be a pinned contiguous float32 host tensor of the shape of am_scores");
-        if (staged) out_dev = torch::empty(am_scores.sizes(), dev_opts);
     } else {
         out = torch::empty(am_scores.sizes(), dev_opts);
     }
@@ -202,6 +204,17 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
     torch::Tensor work  = byte_buffer(wbytes, edges.device());
     torch::Tensor loss2 = torch::empty({2}, dev_opts);
     // pinned host memory is addressable from the device under unified addressing
+    const bool sparse_rows = p.summary.max_slots * 16 <= p.summary.F;
+    if (out_pinned.has_value() && staged && sparse_rows) {
+        const size_t hbytes = fbw_b200_run_to_host_bytes(&p.summary);
+        torch::Tensor host_work = torch::empty({(int64_t)hbytes}, torch::TensorOptions().dtype(torch::kUInt8).pinned_memory(true));
+        check_status(fbw_b200_run_to_host(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
+                                          out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
+                                          work.data_ptr(), wbytes, host_work.data_ptr(), hbytes,
+                                          reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+        return {out, sums, loss2};
+    }
+    if (out_pinned.has_value() && staged) out_dev = torch::empty(am_scores.sizes(), dev_opts);
     if (out_dev.defined()) {
         check_status(fbw_b200_run_host_out(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
                                            out_dev.data_ptr<float>(), out.data_ptr<float>(),

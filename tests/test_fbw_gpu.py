@@ -238,8 +238,11 @@ def test_fused_wrapper_matches_plain_wrapper(fbw_mod, cuda, name, kw):
 def test_scores_in_pinned_host_memory(fbw_mod, cuda):
     """The op may read its scores in place from pinned host memory (the gather fetches the sectors it
     needs over the bus): bit-identical to the run on a device copy, small case and pipelined case."""
-    for name, kw in [("monophone", dict()), ("triphone", dict(B=8, T=1500, F=12001))]:
+    for name, kw, bad in [("monophone", dict(), None), ("triphone", dict(B=8, T=1500, F=12001), None),
+                          ("triphone", dict(B=6, T=400, F=12001), 2)]:
         b = wl.make_batch(name, **kw)
+        if bad is not None:
+            b.seq_lens[bad] = 0  # an invalid length: rows of +inf, written without posteriors
         am = wl.make_scores(b, cuda)
         fsa, sl = wl.to_torch(b, cuda)
         am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
@@ -249,8 +252,10 @@ def test_scores_in_pinned_host_memory(fbw_mod, cuda):
         torch.cuda.synchronize()
         assert out_h.is_cuda and torch.equal(sums_h, sums) and torch.equal(out_h, out)
         assert abs(float(loss2[0]) - float(sums.double().sum())) <= 1e-4 * abs(float(sums.double().sum()))
-        # the result delivered into a pinned host tensor: copied out piece by piece while the op runs
-        # (staged), or written in place by the output pass
+        # the result delivered into a pinned host tensor.  staged: sparse rows (the triphone cases, as a
+        # pipeline over time chunks and as a single launch sequence) are written by host threads from
+        # the posteriors the device sends, dense rows are copied out piece by piece while the op runs;
+        # not staged: written in place by the device's output pass
         for staged in (True, False):
             out_p = torch.full(am.shape, float("nan"), dtype=am.dtype).pin_memory()
             got, sums_p, _ = fbw_mod.fbw_host_scores(am_h, fsa, sl, out=out_p, staged=staged)
