@@ -124,10 +124,12 @@ def fbw_host_scores(am_scores_pinned, fsa, seq_lens, out=None, staged=True):
     a whole; the gather kernel fetches the ones the automata refer to over the bus (about a quarter of
     the tensor on the triphone workload).  ``out``: an optional pinned host tensor of the same shape
     that receives the (T,B,F) result; without it ``out`` is a new device tensor.  With
-    ``staged=True`` (default) the result is produced in a temporary device buffer and every finished
-    part of it is copied to ``out`` while the rest is still being computed; with ``staged=False`` the
-    output pass writes straight into ``out`` and no device copy of the result exists (saves its HBM,
-    slower over the bus).
+    ``staged=True`` (default) the library picks the faster way over the bus: where the rows are sparse
+    only the class posteriors are sent and host threads of the library write the rows into ``out``
+    while the device goes on (the call then returns when ``out`` is complete); dense rows are produced
+    in a temporary device buffer and every finished part is copied to ``out`` while the rest is still
+    being computed.  With ``staged=False`` the device's output pass writes straight into ``out``
+    (slower over the bus).  No device copy of the result is kept in any of the three.
     ``sum_output`` and ``loss2`` are device tensors.  Results are bit-identical to ``core.fbw`` on a
     device copy.  No counterpart in the reference, whose op requires CUDA tensors."""
     num_states, edge_tensor, weight_tensor, start_end_states = fsa

@@ -110,8 +110,9 @@ def sharded_fbw(am_scores, fsa, seq_lens, plan=None, group=None):
 def sharded_fbw_host_scores(am_scores_pinned, fsa, seq_lens, group=None, out=None, staged=True):
     """:func:`sharded_fbw` for scores that live in pinned host memory: the op reads the scores it needs
     in place (no copy of the whole tensor to the device); ``out``, if given, is a pinned host tensor
-    that receives the (T,B,F) result (``staged``: through a device buffer, copied out while the op
-    runs; otherwise written in place by the output pass).  Returns (out, sums, loss2_global).  An empty
+    that receives the (T,B,F) result (``staged``: sparse rows are written by the library's host threads
+    from the posteriors the device sends, dense ones go through a device buffer that is copied out while
+    the op runs; otherwise written in place by the output pass).  Returns (out, sums, loss2_global).  An empty
     shard is handled as in :func:`sharded_fbw`."""
     num_states, edges, weights, start_end = fsa
     if am_scores_pinned.shape[1] == 0:
