@@ -845,6 +845,9 @@ struct RunArgs {
     // do nothing else -- and k_patch writes the posteriors into it.  The word counts the rows taken.
     unsigned long long* next_row;
     int fill_ctas;
+    // 1: the frame-major score array Gf has been filled by the host (fbw_b200_run_with_host with scores in
+    // host memory); k_gather then only builds the tiled copy from it
+    int gathered_by_host;
 };
 
 // chunk in which the sweeps first need the scores of tile k of a sequence of Te frames: the forward
@@ -899,24 +902,26 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
         for (int f = warp; f < kTile; f += 8) {
             const int  t     = k * kTile + f;
             const bool valid = t < Te;
-            const float* __restrict__ row =
-                a.am + (a.fused ? ((i64)b * a.T + t) : ((i64)t * B + b)) * a.F;
+            // (scores gathered by the host: the row of Gf itself, indexed by slot)
+            const float* row = a.gathered_by_host
+                                   ? gf + (i64)t * Dp + d0
+                                   : a.am + (a.fused ? ((i64)b * a.T + t) : ((i64)t * B + b)) * a.F;
             const float sgn = a.fused == 1 ? -1.f : 1.f;  // 2: batch-major input, sign kept
             float v[kGatherSlots / 32];
 #pragma unroll
             for (int j = 0; j < kGatherSlots / 32; j++) {
                 int dd = lane + 32 * j;
-                v[j]   = (valid && dd < nd) ? sgn * __ldg(row + em[j]) : CUDART_INF_F;
+                v[j]   = (valid && dd < nd) ? (a.gathered_by_host ? row[dd] : sgn * __ldg(row + em[j])) : CUDART_INF_F;
             }
 #pragma unroll
             for (int j = 0; j < kGatherSlots / 32; j++) {
                 int dd = lane + 32 * j;
                 if (dd < nd) {
                     tile[f][dd] = v[j];
-                    if (valid) gf[(i64)t * Dp + d0 + dd] = v[j];
+                    if (valid && !a.gathered_by_host) gf[(i64)t * Dp + d0 + dd] = v[j];
                 }
             }
-            if (valid && c == nch - 1) {
+            if (valid && c == nch - 1 && !a.gathered_by_host) {
                 for (int dd = Db + lane; dd < Dp; dd += 32) gf[(i64)t * Dp + dd] = 0.f;
             }
         }
@@ -1702,9 +1707,9 @@ RunLayout run_layout(const fbw_b200_summary& s) {
     return L;
 }
 
-// pinned host scratch of fbw_b200_run_to_host: the plan arrays the host threads read and the posteriors
+// pinned host scratch of fbw_b200_run_with_host: the plan arrays the host threads read and the posteriors
 struct HostLayout {
-    size_t seq_T, nslot, slot_off, gf_off, slot_emis, P, total;
+    size_t seq_T, nslot, slot_off, gf_off, slot_emis, P, G, total;
 };
 
 HostLayout host_layout(const fbw_b200_summary& s) {
@@ -1721,6 +1726,7 @@ HostLayout host_layout(const fbw_b200_summary& s) {
     H.gf_off    = take(8 * (size_t)s.B);
     H.slot_emis = take(4 * (size_t)(s.E + s.B + 1));  // the plan's array: a sequence's classes start at slot_off[b] <= E
     H.P         = take(4 * ((size_t)s.frame_floats + 8));
+    H.G         = take(4 * ((size_t)s.frame_floats + 8));  // scores gathered by the host
     H.total     = off;
     return H;
 }
@@ -1755,6 +1761,7 @@ void plan_args(RunArgs& a, const void* plan, const fbw_b200_summary& s) {
     a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
     a.next_row = nullptr;
     a.fill_ctas = 0;
+    a.gathered_by_host = 0;
 }
 
 // the arguments of one forward-backward call: plan arrays, run scratch, inputs and outputs
@@ -1890,7 +1897,7 @@ struct StreamPool {
     cudaStream_t aux[FBW_B200_GROUPS];
     cudaStream_t copy;  // device -> host copies of finished parts of the output
     cudaEvent_t  fork, join[FBW_B200_GROUPS], copied;
-    // fbw_b200_run_to_host: one such call per device at a time (its thread waits on these events)
+    // fbw_b200_run_with_host: one such call per device at a time (its thread waits on these events)
     std::mutex   host_mu;
     cudaEvent_t  host_ready, host_done[kMaxChunks];
     cudaEvent_t  gathered[kMaxChunks], swept[kMaxChunks], expanded[kMaxChunks];
@@ -2332,11 +2339,14 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
                     fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0,
-                    float* out_host = nullptr, void* host_work = nullptr) {
-    // host_work (fbw_b200_run_to_host, sparse rows): `out` IS the pinned host buffer.  No kernel
-    // composes rows: the class posteriors go to pinned host memory (in host_work) as the posterior
-    // stages finish, and host threads write the rows from them (host_fill.cpp) while the device goes on.
-    const bool host_patch = host_work != nullptr;
+                    float* out_host = nullptr, void* host_work = nullptr, bool host_writes_rows = false) {
+    // host_work (fbw_b200_run_with_host): pinned host scratch; host threads of the library take over what
+    // is slow over the bus (host_fill.cpp).  Scores in host memory: they pick the scores the automata
+    // need out of the tensor.  host_writes_rows (sparse rows): `out` IS a pinned host buffer and no
+    // kernel composes rows; the class posteriors go to pinned host memory as the posterior stages
+    // finish, and the host threads write the rows from them while the device goes on.
+    const bool host_help  = host_work != nullptr;
+    const bool host_patch = host_help && host_writes_rows;
     if (!plan || !summary || !am || !out || !sums || !work) return FBW_B200_BAD_ARGUMENT;
     if (summary->error) return FBW_B200_BAD_AUTOMATON;
     if (((uintptr_t)out & 15) != 0 || ((uintptr_t)work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
@@ -2348,10 +2358,10 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     a.keep_dead_states = keep_dead_states;
     fbw_b200::HostRows host_rows;
     const HostLayout H = host_layout(s);
-    StreamPool* host_pool = host_patch ? stream_pool() : nullptr;
+    StreamPool* host_pool = host_help ? stream_pool() : nullptr;
     std::unique_lock<std::mutex> host_lock;
     int  host_first_chunk = 0, host_chunks = 0;
-    if (host_patch) {
+    if (host_help) {
         if (fused || out_host) return FBW_B200_BAD_ARGUMENT;
         if (!host_pool) return FBW_B200_CUDA_ERROR;
         host_lock = std::unique_lock<std::mutex>(host_pool->host_mu);
@@ -2365,7 +2375,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         CUDA_OK(cudaMemcpyAsync(hw + H.slot_emis, at<int>(plan, L.slot_emis), 4 * (size_t)(s.E + s.B + 1),
                                 cudaMemcpyDeviceToHost, st));
         CUDA_OK(cudaEventRecord(host_pool->host_ready, st));
-        a.P = reinterpret_cast<float*>(hw + H.P);
+        if (host_patch) a.P = reinterpret_cast<float*>(hw + H.P);
         host_rows.T = s.T; host_rows.B = s.B; host_rows.F = s.F;
         host_rows.seq_T     = reinterpret_cast<const int*>(hw + H.seq_T);
         host_rows.nslot     = reinterpret_cast<const int*>(hw + H.nslot);
@@ -2374,12 +2384,13 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         host_rows.slot_emis = reinterpret_cast<const int*>(hw + H.slot_emis);
         host_rows.P   = a.P;
         host_rows.out = out;
+        host_rows.am  = nullptr;
         host_rows.chunk_steps = 1 << 30;
         host_rows.first_chunk = 0;
         host_rows.num_slots = s.E + s.B + 1;
         host_rows.p_floats  = s.frame_floats;
     }
-    const int host_nthreads = host_patch ? fbw_b200::host_threads() : 0;
+    const int host_nthreads = host_help ? fbw_b200::host_threads() : 0;
     // the stages every schedule below runs for a group of sequences or a time chunk
     const int kStages = host_patch ? (kDoGather | kDoSweep | kDoPost) : kDoAll;
 
@@ -2414,6 +2425,23 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             (void)cudaGetLastError();
         }
         if (host_patch && !a.out_plain) return FBW_B200_BAD_ARGUMENT;
+    }
+    if (host_help && host_scores) {
+        // Scores in host memory: reading the sectors the automata need over the bus takes 37 ms on the
+        // triphone workload (32-byte read requests), and nothing else of the call can start before.  The
+        // host threads pick them out of the tensor instead (a cache line per class, 13 ms) and one copy
+        // takes the 92 MB to the device; k_gather then only builds the tiled copy.
+        static int conf = -1;
+        if (conf < 0) { const char* e = getenv("FBW_B200_HOST_GATHER"); conf = e ? atoi(e) : 1; }
+        if (conf) {
+            CUDA_OK(cudaEventSynchronize(host_pool->host_ready));
+            host_rows.am = am;
+            float* G = reinterpret_cast<float*>(static_cast<char*>(host_work) + H.G);
+            if (!fbw_b200::host_gather(host_rows, G, host_nthreads)) return FBW_B200_BAD_ARGUMENT;
+            CUDA_OK(cudaMemcpyAsync(a.Gf, G, 4 * (size_t)s.frame_floats, cudaMemcpyHostToDevice, st));
+            a.gathered_by_host = 1;
+            host_scores = false;  // from here on the call is one whose scores are on the device
+        }
     }
     int G = ev ? 1 : choose_groups(s);
     if (G > 1 && host_scores && !(s.max_edges >= 2048 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E)) G = 1;
@@ -2630,10 +2658,16 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             host_chunks = 1;
         }
         CUDA_OK(cudaEventSynchronize(host_pool->host_ready));
+        const bool dbg = getenv("FBW_B200_HOST_DEBUG") != nullptr;
+        auto now_ms = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
+        const double t_start = now_ms();
         bool rows_ok = fbw_b200::host_compose(host_rows, -1, host_nthreads);
+        if (dbg) fprintf(stderr, "host: padding rows done at %.1f ms\n", now_ms() - t_start);
         for (int c = host_first_chunk; c < host_chunks; c++) {
             CUDA_OK(cudaEventSynchronize(host_pool->host_done[c]));
+            const double t_ready = now_ms();
             rows_ok = fbw_b200::host_compose(host_rows, c, host_nthreads) && rows_ok;
+            if (dbg) fprintf(stderr, "host: chunk %d ready at %.1f ms, written at %.1f ms\n", c, t_ready - t_start, now_ms() - t_start);
         }
         if (!rows_ok) return FBW_B200_BAD_ARGUMENT;
     }
@@ -2675,31 +2709,35 @@ int fbw_b200_run_host_out(const void* plan, const fbw_b200_summary* summary, con
     return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, out_host);
 }
 
-size_t fbw_b200_run_to_host_bytes(const fbw_b200_summary* summary) {
+size_t fbw_b200_run_with_host_bytes(const fbw_b200_summary* summary) {
     if (!summary) return 0;
     return host_layout(*summary).total;
 }
 
-int fbw_b200_run_to_host(const void* plan, const fbw_b200_summary* summary, const float* am, float* out_host,
-                         float* sums, float* loss2, void* work, size_t work_bytes, void* host_work,
-                         size_t host_work_bytes, fbw_b200_stream_t stream) {
-    if (!summary || !out_host) return FBW_B200_BAD_ARGUMENT;
+int fbw_b200_run_with_host(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                           float* sums, float* loss2, void* work, size_t work_bytes, void* host_work,
+                           size_t host_work_bytes, fbw_b200_stream_t stream) {
+    if (!summary || !out || !am) return FBW_B200_BAD_ARGUMENT;
+    if (!host_work || ((uintptr_t)host_work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
+    if (host_work_bytes < host_layout(*summary).total) return FBW_B200_WORKSPACE;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host_work) != cudaSuccess || attr.type != cudaMemoryTypeHost) {
+        (void)cudaGetLastError();
+        return FBW_B200_BAD_ARGUMENT;  // has to be pinned: the device reads and writes it
+    }
+    bool out_on_host = false;
+    if (cudaPointerGetAttributes(&attr, out) == cudaSuccess) {
+        out_on_host = attr.type == cudaMemoryTypeHost;
+    } else {
+        (void)cudaGetLastError();
+    }
     i64 ms, me, md;
     plan_maxima(*summary, ms, me, md);
     static int conf = -1;  // FBW_B200_HOST_ROWS=0: always let the device's output pass write the rows
     if (conf < 0) { const char* e = getenv("FBW_B200_HOST_ROWS"); conf = e ? atoi(e) : 1; }
-    const bool sparse = conf && md * 16 <= summary->F && ((uintptr_t)out_host & 3) == 0;
-    if (sparse) {
-        if (!host_work || ((uintptr_t)host_work & 255) != 0) return FBW_B200_BAD_ARGUMENT;
-        if (host_work_bytes < host_layout(*summary).total) return FBW_B200_WORKSPACE;
-        cudaPointerAttributes attr;
-        if (cudaPointerGetAttributes(&attr, host_work) != cudaSuccess || attr.type != cudaMemoryTypeHost) {
-            (void)cudaGetLastError();
-            return FBW_B200_BAD_ARGUMENT;  // has to be pinned: the device writes the posteriors there
-        }
-    }
-    return run_impl(plan, summary, am, out_host, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, nullptr,
-                    sparse ? host_work : nullptr);
+    const bool rows_by_host = conf && out_on_host && md * 16 <= summary->F;
+    return run_impl(plan, summary, am, out, sums, loss2, work, work_bytes, stream, nullptr, 0, 0, nullptr, host_work,
+                    rows_by_host);
 }
 
 int fbw_b200_run_phases(const void* plan, const fbw_b200_summary* summary, const float* am,

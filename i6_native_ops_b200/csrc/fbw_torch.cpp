@@ -184,7 +184,7 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
     if (out_pinned.has_value()) {
         // The (T,B,F) result ends up in the caller's pinned host tensor.  staged: the library picks the
         // faster way over the bus -- where the rows are sparse, only the class posteriors are sent and
-        // host threads write the rows from them while the device goes on (fbw_b200_run_to_host; the
+        // host threads write the rows from them while the device goes on (fbw_b200_run_with_host; the
         // call then returns when the rows are written); else the result is produced in a device buffer
         // and copied out piece by piece while the rest is still being computed.  Not staged: the
         // output pass writes every row straight into host memory.  No device copy of the result is
@@ -205,13 +205,18 @@ std::vector<torch::Tensor> fbw_host_scores(torch::Tensor& am_scores, torch::Tens
     torch::Tensor loss2 = torch::empty({2}, dev_opts);
     // pinned host memory is addressable from the device under unified addressing
     const bool sparse_rows = p.summary.max_slots * 16 <= p.summary.F;
-    if (out_pinned.has_value() && staged && sparse_rows) {
-        const size_t hbytes = fbw_b200_run_to_host_bytes(&p.summary);
+    // Host threads of the library help where the rows are sparse: they pick the scores the automata
+    // need out of the pinned tensor (instead of 32-byte reads over the bus) and, for a result in host
+    // memory, write its rows from the posteriors the device sends.  Small calls are not worth the threads.
+    const bool with_host = sparse_rows && (double)am_scores.numel() >= 1.0e7 &&
+                           (out_pinned.has_value() ? staged : true);
+    if (with_host) {
+        const size_t hbytes = fbw_b200_run_with_host_bytes(&p.summary);
         torch::Tensor host_work = torch::empty({(int64_t)hbytes}, torch::TensorOptions().dtype(torch::kUInt8).pinned_memory(true));
-        check_status(fbw_b200_run_to_host(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
-                                          out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
-                                          work.data_ptr(), wbytes, host_work.data_ptr(), hbytes,
-                                          reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+        check_status(fbw_b200_run_with_host(p.plan.data_ptr(), &p.summary, am_scores.data_ptr<float>(),
+                                            out.data_ptr<float>(), sums.data_ptr<float>(), loss2.data_ptr<float>(),
+                                            work.data_ptr(), wbytes, host_work.data_ptr(), hbytes,
+                                            reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
         return {out, sums, loss2};
     }
     if (out_pinned.has_value() && staged) out_dev = torch::empty(am_scores.sizes(), dev_opts);

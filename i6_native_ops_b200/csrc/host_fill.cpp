@@ -1,10 +1,11 @@
-// Host side of the result delivery into pinned host memory (fbw_b200_run_to_host).  The (T,B,F)
-// result of a call with few classes per sequence is almost entirely +inf; sending it over the bus
-// costs more than the whole computation.  Instead the device leaves the class posteriors (2 % of the
-// result) in pinned host memory as it computes them, and the threads here write the rows: a row
-// buffer that holds +inf gets the row's posteriors, goes to its place with streaming stores, and
-// has the posteriors taken out again.  No counterpart in the reference, whose outputs are device
-// tensors.
+// Host side of calls whose scores or results live in pinned host memory (fbw_b200_run_with_host).
+// Result: the (T,B,F) result of a call with few classes per sequence is almost entirely +inf; sending
+// it over the bus costs more than the whole computation.  Instead the device leaves the class
+// posteriors (2 % of the result) in pinned host memory as it computes them, and the threads here write
+// the rows: a row buffer that holds +inf gets the row's posteriors, goes to its place with streaming
+// stores, and has the posteriors taken out again.  Scores: the threads pick the entries the automata
+// refer to out of the tensor, which the device would otherwise fetch as 32-byte reads over the bus.
+// No counterpart in the reference, whose inputs and outputs are device tensors.
 #include "host_fill.h"
 
 #include <emmintrin.h>
@@ -105,6 +106,59 @@ void worker(const HostRows* hp, int chunk, std::atomic<int64_t>* next, std::atom
 }
 
 }  // namespace
+
+namespace {
+
+void gather_worker(const HostRows* hp, float* G, std::atomic<int64_t>* next, std::atomic<int>* bad) {
+    const HostRows& h = *hp;
+    const int64_t rows = h.T * h.B;
+    const int64_t batch = 16;
+    for (;;) {
+        const int64_t r0 = next->fetch_add(batch);
+        if (r0 >= rows) break;
+        const int64_t r1 = r0 + batch < rows ? r0 + batch : rows;
+        for (int64_t r = r0; r < r1; r++) {
+            const int64_t t = r / h.B;
+            const int b = (int)(r - t * h.B);
+            if (t >= h.seq_T[b]) continue;
+            const int Db = h.nslot[b], Dp = (Db + 3) & ~3;
+            const int64_t so = h.slot_off[b], po = h.gf_off[b] + t * (int64_t)Dp;
+            if (Db < 0 || so < 0 || so + Db > h.num_slots || po < 0 || po + Dp > h.p_floats) {
+                bad->store(1);
+                continue;
+            }
+            const int* emis = h.slot_emis + so;
+            const float* row = h.am + r * h.F;
+            float* g = G + po;
+            // the reads are the cost (a cache line of the score row per class): ask for them ahead
+            for (int d = 0; d < Db && d < 16; d++) _mm_prefetch(reinterpret_cast<const char*>(row + emis[d]), _MM_HINT_NTA);
+            for (int d = 0; d < Db; d++) {
+                if (d + 16 < Db) _mm_prefetch(reinterpret_cast<const char*>(row + emis[d + 16]), _MM_HINT_NTA);
+                const int e = emis[d];
+                if (e < 0 || e >= h.F) {
+                    bad->store(1);
+                    break;
+                }
+                g[d] = row[e];
+            }
+            for (int d = Db; d < Dp; d++) g[d] = 0.f;
+        }
+    }
+}
+
+}  // namespace
+
+bool host_gather(const HostRows& h, float* G, int threads) {
+    if (threads < 1) threads = 1;
+    std::atomic<int64_t> next{0};
+    std::atomic<int> bad{0};
+    std::vector<std::thread> pool;
+    pool.reserve((size_t)threads - 1);
+    for (int i = 1; i < threads; i++) pool.emplace_back(gather_worker, &h, G, &next, &bad);
+    gather_worker(&h, G, &next, &bad);
+    for (auto& th : pool) th.join();
+    return bad.load() == 0;
+}
 
 bool host_compose(const HostRows& h, int chunk, int threads) {
     if (threads < 1) threads = 1;

@@ -21,6 +21,7 @@ struct HostRows {
     const int*     slot_emis;  // classes, ascending per sequence
     const float*   P;          // posteriors [sequence][frame][slot, padded to 4]
     float*         out;        // (T,B,F)
+    const float*   am;         // scores (T,B,F), for host_gather (may be null otherwise)
     int chunk_steps;           // frames the sweeps advance per time chunk (1 << 30: one chunk)
     int first_chunk;           // first chunk whose posterior stages ran
     int64_t num_slots, p_floats;  // capacity of slot_emis and of P (the indices above are checked against them)
@@ -36,5 +37,11 @@ int host_row_chunk(const HostRows& h, int64_t t, int b);
 // Returns false, with the offending rows left unwritten, if an index of the plan arrays points outside
 // slot_emis, P or the row (which a plan accepted by fbw_b200_plan_summary never does).
 bool host_compose(const HostRows& h, int chunk, int threads);
+
+// The scores the automata refer to, picked out of h.am by `threads` host threads:
+// G[gf_off[b] + t * Dp + d] = am[t][b][class d of sequence b] for every valid frame, 0 in the padding
+// slots (Dp = slots padded to 4), the layout of the device's frame-major score array.  Returns false
+// on an index outside the arrays (see host_compose).
+bool host_gather(const HostRows& h, float* G, int threads);
 
 }  // namespace fbw_b200

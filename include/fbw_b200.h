@@ -141,24 +141,28 @@ int fbw_b200_run_host_out(const void* plan, const fbw_b200_summary* summary, con
                           float* out_host, float* sums, float* loss2, void* work, size_t work_bytes,
                           fbw_b200_stream_t stream);
 
-/* fbw_b200_run for callers whose results live in host memory and who need no device copy of them:
- * `out_host` is a PINNED HOST buffer of T*B*F floats (device-accessible under unified addressing) that
- * receives the (T,B,F) result; `sums`, `loss2` and everything else as in fbw_b200_run.  Where the rows
- * are sparse (few classes per sequence against F) sending the result over the bus would cost more than
- * computing it, and nearly all of it is +inf.  The device then sends only the class posteriors (2 % of
- * the result on the triphone workload), into `host_work`, as its posterior stages finish, and host
- * threads of this library (as many as the process may use, at most 16; FBW_B200_HOST_THREADS) write
- * the rows from them while the device goes on.  `host_work`: PINNED HOST scratch, 256-byte aligned, of
- * fbw_b200_run_to_host_bytes(summary) bytes, the caller's as all scratch is.  THE CALL BLOCKS until the
- * rows are written, so `out_host` is complete when it returns; `sums` and `loss2` are complete when
- * `stream` has been synchronised, as for every other entry.  One such call per device at a time
- * (others wait).  Dense rows are written whole by the device's output pass, straight into `out_host`,
- * without blocking and without `host_work`.  Same bits as fbw_b200_run.  No counterpart in the
- * reference, whose outputs are device tensors. */
-size_t fbw_b200_run_to_host_bytes(const fbw_b200_summary* summary);
-int fbw_b200_run_to_host(const void* plan, const fbw_b200_summary* summary, const float* am, float* out_host,
-                         float* sums, float* loss2, void* work, size_t work_bytes, void* host_work,
-                         size_t host_work_bytes, fbw_b200_stream_t stream);
+/* fbw_b200_run for callers whose scores and/or results live in PINNED HOST memory, with host threads of
+ * this library (as many as the process may use, at most 16; FBW_B200_HOST_THREADS) taking over what is
+ * slow over the bus.  Arguments as fbw_b200_run; `am` and `out` may each be device memory or pinned host
+ * memory (device-accessible under unified addressing); `host_work`: PINNED HOST scratch, 256-byte
+ * aligned, of fbw_b200_run_with_host_bytes(summary) bytes, the caller's as all scratch is.
+ *   Scores in host memory: the device would fetch the entries the automata refer to as 32-byte reads
+ * over the bus, and nothing else of the call can start before.  The host threads pick them out of the
+ * tensor instead and one copy takes them to the device (triphone workload: 14 ms against 37 ms).
+ *   Result in host memory, sparse rows (few classes per sequence against F): sending the (T,B,F) result
+ * over the bus would cost more than computing it, and nearly all of it is +inf.  The device sends only
+ * the class posteriors (2 % of the result on the triphone workload), into `host_work`, as its posterior
+ * stages finish, and the host threads write the rows from them while the device goes on.  Dense rows
+ * are written whole by the device's output pass, straight into `out`.
+ * THE CALL BLOCKS while the host threads work: with scores in host memory before the device work is
+ * enqueued, with host-written rows until they are written, so that a host `out` is complete when the
+ * call returns; `sums`, `loss2` and a device `out` are complete when `stream` has been synchronised, as
+ * for every other entry.  One such call per device at a time (others wait).  Same bits as fbw_b200_run.
+ * No counterpart in the reference, whose inputs and outputs are device tensors. */
+size_t fbw_b200_run_with_host_bytes(const fbw_b200_summary* summary);
+int fbw_b200_run_with_host(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
+                           float* sums, float* loss2, void* work, size_t work_bytes, void* host_work,
+                           size_t host_work_bytes, fbw_b200_stream_t stream);
 
 /* fbw_b200_run with the Python wrapper's elementwise passes folded in (the steps either side of the
  * op in i6_native_ops/fbw/__init__.py:41-44 and :66): the input is log_probs in the caller's own
