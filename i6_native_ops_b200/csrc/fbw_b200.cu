@@ -2336,6 +2336,35 @@ size_t fbw_b200_run_bytes(const fbw_b200_summary* summary) {
     return run_layout(*summary).total;
 }
 
+// The plan arrays the host threads read, copied into the pinned scratch behind `st` (complete when
+// `ready` has happened), and `h` pointed at them.
+static int host_plan_arrays(const void* plan, const fbw_b200_summary& s, char* hw, const HostLayout& H,
+                            cudaStream_t st, cudaEvent_t ready, fbw_b200::HostRows& h) {
+    const PlanLayout L = plan_layout(s.B, s.E, s.S);
+    CUDA_OK(cudaMemcpyAsync(hw + H.seq_T, at<int>(plan, L.seq_T), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaMemcpyAsync(hw + H.nslot, at<int>(plan, L.nslot), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaMemcpyAsync(hw + H.slot_off, at<int>(plan, L.slot_off), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaMemcpyAsync(hw + H.gf_off, at<i64>(plan, L.gf_off), 8 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaMemcpyAsync(hw + H.slot_emis, at<int>(plan, L.slot_emis), 4 * (size_t)(s.E + s.B + 1),
+                            cudaMemcpyDeviceToHost, st));
+    CUDA_OK(cudaEventRecord(ready, st));
+    h.T = s.T; h.B = s.B; h.F = s.F;
+    h.seq_T     = reinterpret_cast<const int*>(hw + H.seq_T);
+    h.nslot     = reinterpret_cast<const int*>(hw + H.nslot);
+    h.slot_off  = reinterpret_cast<const int*>(hw + H.slot_off);
+    h.gf_off    = reinterpret_cast<const int64_t*>(hw + H.gf_off);
+    h.slot_emis = reinterpret_cast<const int*>(hw + H.slot_emis);
+    h.P   = nullptr;
+    h.out = nullptr;
+    h.am  = nullptr;
+    h.batch_major = 0;
+    h.chunk_steps = 1 << 30;
+    h.first_chunk = 0;
+    h.num_slots = s.E + s.B + 1;
+    h.p_floats  = s.frame_floats;
+    return FBW_B200_OK;
+}
+
 static int run_impl(const void* plan, const fbw_b200_summary* summary, const float* am, float* out,
                     float* sums, float* loss2, void* work, size_t work_bytes,
                     fbw_b200_stream_t stream, cudaEvent_t* ev, int fused = 0, int keep_dead_states = 0,
@@ -2366,29 +2395,12 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
         if (!host_pool) return FBW_B200_CUDA_ERROR;
         host_lock = std::unique_lock<std::mutex>(host_pool->host_mu);
         // the little the host has to know about the plan, and the posteriors' place in host memory
-        const PlanLayout L = plan_layout(s.B, s.E, s.S);
         char* hw = static_cast<char*>(host_work);
-        CUDA_OK(cudaMemcpyAsync(hw + H.seq_T, at<int>(plan, L.seq_T), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
-        CUDA_OK(cudaMemcpyAsync(hw + H.nslot, at<int>(plan, L.nslot), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
-        CUDA_OK(cudaMemcpyAsync(hw + H.slot_off, at<int>(plan, L.slot_off), 4 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
-        CUDA_OK(cudaMemcpyAsync(hw + H.gf_off, at<i64>(plan, L.gf_off), 8 * (size_t)s.B, cudaMemcpyDeviceToHost, st));
-        CUDA_OK(cudaMemcpyAsync(hw + H.slot_emis, at<int>(plan, L.slot_emis), 4 * (size_t)(s.E + s.B + 1),
-                                cudaMemcpyDeviceToHost, st));
-        CUDA_OK(cudaEventRecord(host_pool->host_ready, st));
+        const int rc = host_plan_arrays(plan, s, hw, H, st, host_pool->host_ready, host_rows);
+        if (rc != FBW_B200_OK) return rc;
         if (host_patch) a.P = reinterpret_cast<float*>(hw + H.P);
-        host_rows.T = s.T; host_rows.B = s.B; host_rows.F = s.F;
-        host_rows.seq_T     = reinterpret_cast<const int*>(hw + H.seq_T);
-        host_rows.nslot     = reinterpret_cast<const int*>(hw + H.nslot);
-        host_rows.slot_off  = reinterpret_cast<const int*>(hw + H.slot_off);
-        host_rows.gf_off    = reinterpret_cast<const int64_t*>(hw + H.gf_off);
-        host_rows.slot_emis = reinterpret_cast<const int*>(hw + H.slot_emis);
         host_rows.P   = a.P;
         host_rows.out = out;
-        host_rows.am  = nullptr;
-        host_rows.chunk_steps = 1 << 30;
-        host_rows.first_chunk = 0;
-        host_rows.num_slots = s.E + s.B + 1;
-        host_rows.p_floats  = s.frame_floats;
     }
     const int host_nthreads = host_help ? fbw_b200::host_threads() : 0;
     // the stages every schedule below runs for a group of sequences or a time chunk

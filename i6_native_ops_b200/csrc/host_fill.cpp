@@ -128,7 +128,7 @@ void gather_worker(const HostRows* hp, float* G, std::atomic<int64_t>* next, std
                 continue;
             }
             const int* emis = h.slot_emis + so;
-            const float* row = h.am + r * h.F;
+            const float* row = h.am + (h.batch_major ? (int64_t)b * h.T + t : r) * h.F;
             float* g = G + po;
             // the reads are the cost (a cache line of the score row per class): ask for them ahead
             for (int d = 0; d < Db && d < 16; d++) _mm_prefetch(reinterpret_cast<const char*>(row + emis[d]), _MM_HINT_NTA);

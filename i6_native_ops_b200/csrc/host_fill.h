@@ -21,7 +21,8 @@ struct HostRows {
     const int*     slot_emis;  // classes, ascending per sequence
     const float*   P;          // posteriors [sequence][frame][slot, padded to 4]
     float*         out;        // (T,B,F)
-    const float*   am;         // scores (T,B,F), for host_gather (may be null otherwise)
+    const float*   am;         // scores, for host_gather (may be null otherwise): (T,B,F), or
+    int            batch_major;  // (B,T,F) if set (the Viterbi op's other layout)
     int chunk_steps;           // frames the sweeps advance per time chunk (1 << 30: one chunk)
     int first_chunk;           // first chunk whose posterior stages ran
     int64_t num_slots, p_floats;  // capacity of slot_emis and of P (the indices above are checked against them)

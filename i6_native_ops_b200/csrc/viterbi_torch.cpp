@@ -49,6 +49,17 @@ std::vector<torch::Tensor> viterbi_impl(const torch::Tensor& scores_in, const to
     auto   stream = at::cuda::getCurrentCUDAStream();
     size_t wbytes = fbw_b200_viterbi_bytes(&p.summary);
     torch::Tensor work = byte_buffer(wbytes, edges.device());
+    // large calls on scores in host memory with few classes per sequence: host threads of the library
+    // pick the scores the automata need out of the pinned tensor instead of 32-byte reads over the bus
+    if (host_scores && (double)scores_in.numel() >= 1.0e7 && p.summary.max_slots * 16 <= p.summary.F) {
+        const size_t hbytes = fbw_b200_run_with_host_bytes(&p.summary);
+        torch::Tensor host_work = torch::empty({(int64_t)hbytes}, torch::TensorOptions().dtype(torch::kUInt8).pinned_memory(true));
+        check_status(fbw_b200_viterbi_with_host(p.plan.data_ptr(), &p.summary, scores_in.data_ptr<float>(),
+                                                alignment.data_ptr<int32_t>(), scores.data_ptr<float>(),
+                                                batch_major ? 1 : 0, work.data_ptr(), wbytes, host_work.data_ptr(),
+                                                hbytes, reinterpret_cast<fbw_b200_stream_t>(stream.stream())));
+        return {alignment, scores};
+    }
     check_status(fbw_b200_viterbi(p.plan.data_ptr(), &p.summary, scores_in.data_ptr<float>(),
                                   alignment.data_ptr<int32_t>(), scores.data_ptr<float>(),
                                   batch_major ? 1 : 0, work.data_ptr(), wbytes,

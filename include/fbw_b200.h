@@ -191,6 +191,15 @@ int fbw_b200_viterbi(const void* plan, const fbw_b200_summary* summary, const fl
                      int32_t* alignment, float* scores, int batch_major, void* work,
                      size_t work_bytes, fbw_b200_stream_t stream);
 
+/* fbw_b200_viterbi for scores in PINNED HOST memory, with the library's host threads picking the entries
+ * the automata refer to out of the tensor (see fbw_b200_run_with_host, whose scratch size
+ * fbw_b200_run_with_host_bytes also holds here).  The call blocks while they work, before the device work
+ * is enqueued.  Scores in device memory are accepted and handled as by fbw_b200_viterbi.  Same results. */
+int fbw_b200_viterbi_with_host(const void* plan, const fbw_b200_summary* summary, const float* scores_in,
+                               int32_t* alignment, float* scores, int batch_major, void* work,
+                               size_t work_bytes, void* host_work, size_t host_work_bytes,
+                               fbw_b200_stream_t stream);
+
 /* fbw_b200_run with per-phase device timing, for benchmarks and profiles: same arguments and
  * results, plus phase_ms (HOST, FBW_B200_NUM_PHASES floats) = milliseconds of the gather, sweep,
  * posterior, expand and loss-reduction kernels measured with CUDA events on `stream`.

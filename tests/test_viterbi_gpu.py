@@ -244,12 +244,19 @@ def test_full_size_triphone(vit, ref_core, cuda):
 
 
 def test_scores_in_pinned_host_memory(vit, cuda):
-    b = wl.make_batch("bpe_ctc", B=8, T=120, F=1025, scale=0.3)
-    fsa, sl = wl.to_torch(b, cuda)
-    am = -wl.make_scores(b, cuda)
-    am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
-    am_h.copy_(am)
-    a1, s1 = vit.core.fast_viterbi(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
-    a2, s2 = vit.core.fast_viterbi_host_scores(am_h, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
-    torch.cuda.synchronize()
-    assert a2.is_cuda and torch.equal(a1, a2) and torch.equal(s1, s2)
+    """Scores read from pinned host memory: by the device's gather (small case) and, for a large call
+    with few classes per sequence, picked out of the tensor by the library's host threads (the triphone
+    case, with one sequence of invalid length); same alignment and scores as on a device copy."""
+    for name, kw, bad in [("bpe_ctc", dict(B=8, T=120, F=1025, scale=0.3), None),
+                          ("triphone", dict(B=6, T=400, F=12001), 4)]:
+        b = wl.make_batch(name, **kw)
+        if bad is not None:
+            b.seq_lens[bad] = 0
+        fsa, sl = wl.to_torch(b, cuda)
+        am = -wl.make_scores(b, cuda)
+        am_h = torch.empty(am.shape, dtype=am.dtype, pin_memory=True)
+        am_h.copy_(am)
+        a1, s1 = vit.core.fast_viterbi(am, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+        a2, s2 = vit.core.fast_viterbi_host_scores(am_h, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+        torch.cuda.synchronize()
+        assert a2.is_cuda and torch.equal(a1, a2) and torch.equal(s1, s2)
