@@ -154,7 +154,15 @@ bool host_gather(const HostRows& h, float* G, int threads) {
     std::atomic<int> bad{0};
     std::vector<std::thread> pool;
     pool.reserve((size_t)threads - 1);
-    for (int i = 1; i < threads; i++) pool.emplace_back(gather_worker, &h, G, &next, &bad);
+    // (a thread that cannot be started is not an error: the rows are handed out through `next`, and
+    // the threads that do run, this one included, take them all)
+    for (int i = 1; i < threads; i++) {
+        try {
+            pool.emplace_back(gather_worker, &h, G, &next, &bad);
+        } catch (...) {
+            break;
+        }
+    }
     gather_worker(&h, G, &next, &bad);
     for (auto& th : pool) th.join();
     return bad.load() == 0;
@@ -166,7 +174,13 @@ bool host_compose(const HostRows& h, int chunk, int threads) {
     std::atomic<int> bad{0};
     std::vector<std::thread> pool;
     pool.reserve((size_t)threads - 1);
-    for (int i = 1; i < threads; i++) pool.emplace_back(worker, &h, chunk, &next, &bad);
+    for (int i = 1; i < threads; i++) {
+        try {
+            pool.emplace_back(worker, &h, chunk, &next, &bad);
+        } catch (...) {
+            break;  // see host_gather
+        }
+    }
     worker(&h, chunk, &next, &bad);
     for (auto& th : pool) th.join();
     return bad.load() == 0;
