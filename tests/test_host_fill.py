@@ -20,7 +20,13 @@ def shim():
     subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-pthread", "-I", CSRC, "-o", out,
                     os.path.join(ROOT, "tests", "host_fill_shim.cpp"), os.path.join(CSRC, "host_fill.cpp")],
                    check=True)
-    return ctypes.CDLL(out)
+    lib = ctypes.CDLL(out)
+    i32, i64, pi, pl, pf = (ctypes.c_int, ctypes.c_longlong, ctypes.POINTER(ctypes.c_int),
+                            ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_float))
+    lib.shim_compose.argtypes = [i64, i64, i64, pi, pi, pi, pl, pi, i64, pf, i64, pf, i32, i32, i32, i32]
+    lib.shim_gather.argtypes = [i64, i64, i64, pi, pi, pi, pl, pi, i64, pf, i32, pf, i64, i32]
+    lib.shim_row_chunk.argtypes = [i32, i64, i32, i32]
+    return lib
 
 
 def ptr(a, t):
