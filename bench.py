@@ -790,11 +790,14 @@ def main():
                          "scope": "whole op call (all kernels), per GPU"},
             "kernels_ms": {"prepare": prep_ms, "gather": float(phase[0]), "sweep": float(phase[1]),
                            "posterior": float(phase[2]), "expand": float(phase[3]),
-                           "loss": float(phase[4])},
+                           "loss": float(phase[4]),
+                           "note": "every stage once over the whole batch on one stream (one-pass output); the timed "
+                                   "step overlaps the stages and may write its output in two steps instead"},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
             "e2e": e2e,
             "e2e_copy": e2e_copy,
+            "e2e_full": e2e_copy,  # the same leg under its other name: every input and result byte crosses the bus
             "e2e_in_place_out": e2e_in_place,
             "e2e_out_on_device": e2e_dev_out,
             "reference_gpu_op": reference_gpu_op,
