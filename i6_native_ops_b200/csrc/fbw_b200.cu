@@ -17,6 +17,11 @@
 //   k_norm    : per (sequence, 32 frames): the frame normaliser, a serial left fold.
 //   k_class   : per (sequence, 32 frames): the class posteriors.
 //   k_expand  : streams the (T,B,F) output: +inf rows with the few finite posteriors patched in.
+//   k_patch   : large calls with sparse rows write the output in two steps instead: a warp more per
+//               sweep CTA writes the +inf background through the copy engine while the sweeps run
+//               (background_rows), and k_patch puts the posteriors into it as whole 32-byte sectors.
+// For scores and results in pinned host memory the library's host threads (host_fill.cpp) pick the
+// scores out of the tensor and write the result's rows from the posteriors the device sends.
 //
 // Arithmetic is kept in the reference's fp32 operation order wherever that order is deterministic
 // there, because scores grow with t (~2e4 at T=1500, one ulp = 2e-3) and any reassociation shows
@@ -29,9 +34,8 @@
 //     (fbw_op.cu:115-118); state and class accumulations also run in ascending edge index (the
 //     reference's atomics have no defined order; with at most two terms the order is immaterial).
 
-#include "host_fill.h"
-#include <limits>
 #include "fbw_b200.h"
+#include "host_fill.h"
 
 #include <cuda_runtime.h>
 #include <math_constants.h>
