@@ -2462,12 +2462,23 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     int G = ev ? 1 : choose_groups(s);
     if (G > 1 && host_scores && !(s.max_edges >= 2048 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E)) G = 1;
     if (host_patch) G = 1;  // the host's row order follows the time chunks
-    const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     i64 ms, me, md;
     plan_maxima(s, ms, me, md);
-    const bool two_step = G > 1 && !fused && !a.out_plain && (((uintptr_t)out & 31) == 0) &&
-                          output_in_two_steps(s, ms, me, md);
-    if (two_step && G == 8 && !getenv("FBW_B200_NUM_GROUPS")) G = 4;
+    // Output in two steps: four groups, most expensive first.  Large calls that can write their output
+    // that way run as groups whatever their batch size: with the background written during the sweeps
+    // the group schedule beats the time-chunk pipeline also for few sequences (triphone, ms per call,
+    // chunks against groups: 8 sequences 1.35 / 1.28, 16: 1.44 / 1.39, 32: 1.79 / 1.70, 48: 2.21 / 1.97;
+    // BPE-CTC 32 sequences 0.68 / 0.61).
+    const bool groups_forced = getenv("FBW_B200_NUM_GROUPS") != nullptr;
+    const bool can_two_step = !ev && !fused && !a.out_plain && (((uintptr_t)out & 31) == 0) &&
+                              output_in_two_steps(s, ms, me, md);
+    if (can_two_step && G == 1 && !groups_forced && !host_scores && !host_patch && s.B >= 4 &&
+        (double)s.T * (double)s.B * (double)s.F >= 1.0e8) {
+        G = 4;
+    }
+    const bool two_step = G > 1 && can_two_step;
+    if (two_step && G == 8 && !groups_forced) G = 4;
+    const int C = (ev || G > 1) ? 1 : choose_chunks(s);
     // every launch shape is checked before anything is enqueued, so that a call that cannot run
     // fails before it has forked onto the auxiliary streams
     if (s.max_len > 0) {
