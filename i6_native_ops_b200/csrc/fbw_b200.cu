@@ -954,6 +954,9 @@ __device__ __forceinline__ void sweep_sync(int nt) {  // the sweep's threads onl
 }
 
 __device__ __forceinline__ void background_rows(const RunArgs& a, const float* block) {
+    // (`block` holds the background value of the mode: +inf, or 0 for the fused gradient output, whose
+    // rows are ordered (sequence, frame))
+    const float bg = a.fused ? 0.f : CUDART_INF_F;
     const int lane = threadIdx.x & 31;
     const int nb = a.r1 - a.r0;
     const i64 F = a.F;
@@ -966,12 +969,12 @@ __device__ __forceinline__ void background_rows(const RunArgs& a, const float* b
         if (it >= rows) break;
         const i64 t = it / nb;
         const int b = a.order[a.r0 + (int)(it - t * nb)];
-        const i64 rbase = (t * a.B + b) * F;
+        const i64 rbase = (a.fused ? (i64)b * a.T + t : t * a.B + b) * F;
         float* __restrict__ row = a.out + rbase;
         const int head = (int)min((i64)((4 - (rbase & 3)) & 3), F);
         const i64 body_end = head + (((F - head) >> 2) << 2);
-        if (lane < head) row[lane] = CUDART_INF_F;
-        if (lane < F - body_end) row[body_end + lane] = CUDART_INF_F;
+        if (lane < head) row[lane] = bg;
+        if (lane < F - body_end) row[body_end + lane] = bg;
         for (i64 cs = head + (i64)lane * kFillFloats; cs < body_end; cs += 32 * (i64)kFillFloats) {
             const unsigned bytes = (unsigned)(min((i64)kFillFloats, body_end - cs) * 4);
             asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(row + cs), "r"(src),
@@ -1020,7 +1023,7 @@ __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, 
             // (the threads of a warp that writes the background all come here)
             for (int i = (fill_only ? threadIdx.x : threadIdx.x - NT); i < kFillFloats;
                  i += (fill_only ? blockDim.x : 32)) {
-                inf_block[i] = CUDART_INF_F;
+                inf_block[i] = a.fused ? 0.f : CUDART_INF_F;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             if (fill_only) __syncthreads(); else __syncwarp();
@@ -1619,7 +1622,11 @@ __device__ __forceinline__ void patch_row(const RunArgs& a, const PostUnit& p, i
     const int* __restrict__ emis = a.slot_emis + p.so;
     const float* __restrict__ Pr = a.P + a.gf_off[p.b] + (i64)t * p.Dp;
     const i64 F     = a.F;
-    const i64 rbase = ((i64)t * a.B + p.b) * F;  // first word of the row
+    // plain mode: background +inf, values are the negative log posteriors; fused mode: background 0,
+    // values are -posterior, rows ordered (sequence, frame) (see k_expand)
+    const bool  fused = a.fused != 0;
+    const float bg    = fused ? 0.f : CUDART_INF_F;
+    const i64 rbase = (fused ? (i64)p.b * a.T + t : (i64)t * a.B + p.b) * F;  // first word of the row
     float* __restrict__ out = a.out;
     for (int d = lane; d < p.Db; d += 32) {
         const i64 g  = rbase + emis[d];
@@ -1629,12 +1636,12 @@ __device__ __forceinline__ void patch_row(const RunArgs& a, const PostUnit& p, i
         if (s0 >= rbase && s0 + 8 <= rbase + F) {
             float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = CUDART_INF_F;
+            for (int i = 0; i < 8; i++) v[i] = bg;
             for (int k = d; k < p.Db; k++) {
                 const i64 gk = rbase + emis[k];
                 if ((gk >> 3) != sg) break;
                 const int pos = (int)(gk & 7);
-                const float val = Pr[k];
+                const float val = fused ? -expf(-Pr[k]) : Pr[k];
 #pragma unroll
                 for (int i = 0; i < 8; i++) v[i] = (i == pos) ? val : v[i];
             }
@@ -1645,7 +1652,7 @@ __device__ __forceinline__ void patch_row(const RunArgs& a, const PostUnit& p, i
             for (int k = d; k < p.Db; k++) {
                 const i64 gk = rbase + emis[k];
                 if ((gk >> 3) != sg) break;
-                out[gk] = Pr[k];
+                out[gk] = fused ? -expf(-Pr[k]) : Pr[k];
             }
         }
     }
@@ -2470,7 +2477,7 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
     // chunks against groups: 8 sequences 1.35 / 1.28, 16: 1.44 / 1.39, 32: 1.79 / 1.70, 48: 2.21 / 1.97;
     // BPE-CTC 32 sequences 0.68 / 0.61).
     const bool groups_forced = getenv("FBW_B200_NUM_GROUPS") != nullptr;
-    const bool can_two_step = !ev && !fused && !a.out_plain && (((uintptr_t)out & 31) == 0) &&
+    const bool can_two_step = !ev && fused != 2 && !a.out_plain && (((uintptr_t)out & 31) == 0) &&
                               output_in_two_steps(s, ms, me, md);
     if (can_two_step && G == 1 && !groups_forced && !host_scores && !host_patch && s.B >= 4 &&
         (double)s.T * (double)s.B * (double)s.F >= 1.0e8) {

@@ -6,7 +6,7 @@ one per call; ``FBW_B200_OUTPUT=expand`` / ``patch`` fixes the choice for a proc
 child processes here do.  Compared: the bit patterns of ``out`` and ``sums`` (as exact integer sums),
 on calls large enough to run as groups of sequences: rows whose length is not a multiple of four words
 (12001 classes), sequences shorter than T, an invalid length, and the BPE-CTC shape with several sweep
-CTAs per SM.
+CTAs per SM; and the wrapper-fused form of the op on the same cases (gradient output).
 """
 import json
 import os
@@ -36,7 +36,13 @@ for name, kw, bad in json.loads(sys.argv[1]):
     torch.cuda.synchronize()
     t = torch.arange(b.T, device=dev)[:, None]
     pad = t >= sl.to(dev)[None, :].clamp(min=0)
-    res.append(dict(out=int(out.view(torch.int32).to(torch.int64).sum().item()),
+    # the wrapper-fused form of the op (gradient output: background 0, rows ordered (sequence, frame))
+    lp = (-am).transpose(0, 1).contiguous()
+    grad, _ = core.fbw_fused(lp, fsa[1], fsa[2], fsa[3], sl, int(fsa[0]))
+    torch.cuda.synchronize()
+    fused = int(grad.view(torch.int32).to(torch.int64).sum().item())
+    del lp, grad
+    res.append(dict(out=int(out.view(torch.int32).to(torch.int64).sum().item()), fused=fused,
                     sums=int(sums.view(torch.int32).to(torch.int64).sum().item()),
                     finite=int(torch.isfinite(out).sum().item()),
                     pad_ok=bool(torch.isinf(out[pad]).all().item()) and bool((sums[pad] == 0).all().item()),
@@ -45,7 +51,8 @@ for name, kw, bad in json.loads(sys.argv[1]):
 print("RESULT " + json.dumps(res))
 """
 
-CASES = [["triphone", {}, 0], ["triphone", {"B": 66, "T": 333}, 5], ["bpe_ctc", {"B": 128}, 0]]
+CASES = [["triphone", {}, 0], ["triphone", {"B": 66, "T": 333}, 5], ["bpe_ctc", {"B": 128}, 0],
+         ["triphone", {"B": 9}, 3]]
 
 
 def run_child(mode):
@@ -64,5 +71,5 @@ def test_background_then_posteriors_equals_one_pass(cuda):
     for case, a, b, c in zip(CASES, one_pass, two_steps, default):
         assert a["pad_ok"] and b["pad_ok"] and c["pad_ok"], case
         assert a["finite"] > 0, case
-        for key in ("out", "sums", "finite"):
+        for key in ("out", "sums", "finite", "fused"):
             assert a[key] == b[key] == c[key], (case, key, a, b, c)
