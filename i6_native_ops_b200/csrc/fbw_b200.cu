@@ -1955,6 +1955,12 @@ int choose_groups(const fbw_b200_summary& s) {
         forced = e ? atoi(e) : 0;
     }
     if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return s.B >= forced ? forced : 1;
+    // Batches with large automata (more states than a sweep CTA has threads: lattices) run as groups at
+    // every batch size: groups give each range of the cost order its own launch shape and cluster size,
+    // which the time-chunk pipeline cannot (lattice, ms per call, time chunks against four groups: 8
+    // sequences 7.9 / 6.6, 24: 20.3 / 11.4, 48: 26.7 / 13.0).  Four groups up to about 70 sequences (64:
+    // 13.7 ms against 14.9 with eight), eight beyond (80: 14.7 against 18.3 with four).
+    if (s.B >= 4 && s.max_states > 1024) return s.B >= 72 ? 8 : 4;
     if (s.B >= 64 && s.E > 0 && (double)s.max_edges * (double)s.B >= 1.8 * (double)s.E &&
         s.max_edges >= 2048) {
         return 8;

@@ -9,12 +9,17 @@ large or irregular automata reach:
   * the large-vocabulary CTC batch at full size (B=256, T=400, F=10025);
   * a 64-sequence slice of the full-scale lattice batch (the largest piece of it one call of the
     reference op can take: its 32-bit sizes overflow beyond, i6_native_ops/fbw/fbw_op.cu:268-276);
-  * 24 lattice sequences (the pipeline over time chunks with the large-automaton sweeps);
+  * 24 lattice sequences, as four size groups and as the pipeline over time chunks with the
+    large-automaton sweeps;
   * a batch of more than 8192 sequences (grouping by sequence switches to a device-wide sort).
 
 Targets: the fp64 CPU oracle on every sequence (or a sample of eight spread over the cost order) and
 two runs of the reference op on the whole batch; bars in tests/parity_util.py.
 """
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -82,13 +87,25 @@ def test_lattice_slice_of_64(fbw_mod, ref_core, cuda):
     full_parity("lattice_full_scale B=64", fbw_mod, ref_core, b, am, cuda, sample=8)
 
 
-def test_lattice_time_chunk_pipeline(fbw_mod, ref_core, cuda):
-    """24 full-scale lattice sequences: too few for the size-group schedule, large enough for the
-    pipeline over time chunks, so the sweeps (clusters, state scores stored four frames at a time) run
-    as several launches that hand their state vectors on."""
+def test_lattice_few_sequences(fbw_mod, ref_core, cuda):
+    """24 full-scale lattice sequences: four size groups of six sequences, the two most expensive
+    groups as clusters."""
     b = wl.make_batch("lattice", B=24)
     am = wl.make_scores(b, cuda)
-    full_parity("lattice_full_scale B=24 (time chunks)", fbw_mod, ref_core, b, am, cuda, sample=8)
+    full_parity("lattice_full_scale B=24 (four groups)", fbw_mod, ref_core, b, am, cuda, sample=8)
+
+
+def test_lattice_time_chunk_pipeline(cuda):
+    """The same 24 sequences through the pipeline over time chunks, which the library no longer picks
+    for large automata by itself (FBW_B200_NUM_GROUPS=1 switches the size groups off for a process): the
+    sweeps (clusters, state scores stored four frames at a time) then run as several launches that hand
+    their state vectors on.  Runs the test above in a child process."""
+    env = dict(os.environ, FBW_B200_NUM_GROUPS="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-m", "gpu", "-k",
+                        "test_lattice_few_sequences", "-p", "no:cacheprovider"],
+                       env=env, capture_output=True, text=True, timeout=1200,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "1 passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
 def test_more_than_8192_sequences(fbw_mod, cuda):
