@@ -130,3 +130,21 @@ def test_indices_outside_the_arrays_are_refused(shim):
                            p_floats, ptr(out, ctypes.c_float), 1 << 30, 0, 0, 2)
     assert rc == 1
     assert 1 <= shim.shim_threads() <= 64
+
+
+def test_threads_are_shared_out_over_the_processes_of_a_node(shim):
+    """LOCAL_WORLD_SIZE (exported by torchrun) divides the CPUs the process may use; FBW_B200_HOST_THREADS
+    overrides.  Read per call, so the environment can be changed in place."""
+    allowed = len(os.sched_getaffinity(0))
+    saved = {k: os.environ.pop(k, None) for k in ("LOCAL_WORLD_SIZE", "FBW_B200_HOST_THREADS")}
+    try:
+        assert shim.shim_threads() == min(allowed, 16)
+        os.environ["LOCAL_WORLD_SIZE"] = "4"
+        assert shim.shim_threads() == min(max(allowed // 4, 2), 16)
+        os.environ["FBW_B200_HOST_THREADS"] = "3"
+        assert shim.shim_threads() == 3
+    finally:
+        for k, v in saved.items():
+            os.environ.pop(k, None)
+            if v is not None:
+                os.environ[k] = v
