@@ -849,6 +849,8 @@ struct RunArgs {
     // do nothing else -- and k_patch writes the posteriors into it.  The word counts the rows taken.
     unsigned long long* next_row;
     int fill_ctas;
+    int fill_piece;   // floats per bulk store of the background (a multiple of 32, at most kFillFloats)
+    int fill_offset;  // where the block of background starts in the sweep CTA's dynamic shared memory (bytes)
     // 1: the frame-major score array Gf has been filled by the host (fbw_b200_run_with_host with scores in
     // host memory); k_gather then only builds the tiled copy from it
     int gathered_by_host;
@@ -947,7 +949,7 @@ __global__ void __launch_bounds__(256) k_gather(RunArgs a) {
 // store waits for another, and the issue slots stay with the sweep.  Rows are handed out through a
 // counter, so that every SM's copy engine is busy until the group's rows are done.  One warp per row;
 // a row starts at any 4-byte offset: scalar head, 16-byte aligned body in pieces, scalar tail.
-constexpr int kFillFloats = 512;
+constexpr int kFillFloats = 2048;  // largest block of background in shared memory: 8 KB
 
 __device__ __forceinline__ void sweep_sync(int nt) {  // the sweep's threads only (a multiple of 32)
     asm volatile("bar.sync 1, %0;" ::"r"(nt) : "memory");
@@ -975,8 +977,9 @@ __device__ __forceinline__ void background_rows(const RunArgs& a, const float* b
         const i64 body_end = head + (((F - head) >> 2) << 2);
         if (lane < head) row[lane] = bg;
         if (lane < F - body_end) row[body_end + lane] = bg;
-        for (i64 cs = head + (i64)lane * kFillFloats; cs < body_end; cs += 32 * (i64)kFillFloats) {
-            const unsigned bytes = (unsigned)(min((i64)kFillFloats, body_end - cs) * 4);
+        const i64 piece = a.fill_piece;
+        for (i64 cs = head + (i64)lane * piece; cs < body_end; cs += 32 * piece) {
+            const unsigned bytes = (unsigned)(min(piece, body_end - cs) * 4);
             asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(row + cs), "r"(src),
                          "r"(bytes)
                          : "memory");
@@ -1014,14 +1017,15 @@ template <int RING, bool TILED, int KREG, bool PRUNE>
 __global__ void __launch_bounds__(1024) k_sweep(RunArgs a, int smax, int dpmax, int edges_in_smem,
                                                 int nrows) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ __align__(128) float inf_block[kFillFloats];
     const int item = blockIdx.x;
     const int NT = blockDim.x - (a.next_row != nullptr ? 32 : 0);  // the sweep's threads
     if (a.next_row != nullptr) {
         const bool fill_only = item >= 2 * (a.r1 - a.r0);
         if (fill_only || (int)threadIdx.x >= NT) {
             // (the threads of a warp that writes the background all come here)
-            for (int i = (fill_only ? threadIdx.x : threadIdx.x - NT); i < kFillFloats;
+            // the block of background lies behind the sweep's own shared memory (launch_group)
+            float* inf_block = reinterpret_cast<float*>(smem_raw + a.fill_offset);
+            for (int i = (fill_only ? threadIdx.x : threadIdx.x - NT); i < a.fill_piece;
                  i += (fill_only ? blockDim.x : 32)) {
                 inf_block[i] = a.fused ? 0.f : CUDART_INF_F;
             }
@@ -1772,6 +1776,8 @@ void plan_args(RunArgs& a, const void* plan, const fbw_b200_summary& s) {
     a.c_lo = 0; a.c_hi = 1; a.chunk_steps = 1 << 30;
     a.next_row = nullptr;
     a.fill_ctas = 0;
+    a.fill_piece = kFillFloats;
+    a.fill_offset = 0;
     a.gathered_by_host = 0;
 }
 
@@ -2010,7 +2016,7 @@ SweepShape sweep_shape(i64 ms, i64 me, i64 md) {
     c.dpmax = (int)((md + 3) & ~3);
     c.nt    = (int)((ms + 31) & ~31);
     c.nt    = c.nt < 64 ? 64 : (c.nt > 1024 ? 1024 : c.nt);
-    const size_t limit = 227 * 1024 - sizeof(float) * kFillFloats;  // less the kernel's static block
+    const size_t limit = 227 * 1024 - sizeof(float) * kFillFloats - 128;  // room for the block of background
     auto need = [&](int ring, int rows, int in_smem) {
         const size_t spad = rows == 64 ? (size_t)(c.smax | 1) : (size_t)c.smax;
         return (size_t)4 * ring * c.dpmax + 4 * (((size_t)rows * spad + 3) & ~(size_t)3) +
@@ -2054,7 +2060,7 @@ bool output_in_two_steps(const fbw_b200_summary& s, i64 ms, i64 me, i64 md) {
     if (!c.found) return false;
     if (conf == 1) return true;
     if (md * 16 > s.F) return false;  // dense rows: patching would touch most sectors twice
-    const i64 by_smem    = (i64)(227 * 1024) / (i64)(c.smem + sizeof(float) * kFillFloats + 1024);
+    const i64 by_smem    = (i64)(227 * 1024) / (i64)(c.smem + sizeof(float) * 512 + 128 + 1024);
     const i64 by_threads = 2048 / (c.nt + 32);
     const i64 per_sm     = by_smem < by_threads ? (by_smem > 0 ? by_smem : 1) : (by_threads > 0 ? by_threads : 1);
     const i64 waves      = (2 * s.B + per_sm * sm_count() - 1) / (per_sm * sm_count());
@@ -2092,8 +2098,13 @@ int launch_group(RunArgs a, int r0, int r1, i64 ms, i64 me, i64 md, const fbw_b2
         if (!c.found) return FBW_B200_TOO_LARGE;
         const int smax = c.smax, dpmax = c.dpmax, nt = c.nt, ring = c.ring, tiled = c.tiled;
         const int in_smem = c.in_smem;
-        const size_t smem = c.smem;
-        // with the background: a warp more per CTA, and CTAs that do nothing else
+        // with the background: its block behind the sweep's shared memory, a warp more per CTA, and CTAs
+        // that do nothing else
+        size_t smem = c.smem;
+        if (a.next_row != nullptr) {
+            a.fill_offset = (int)((c.smem + 127) & ~(size_t)127);
+            smem = (size_t)a.fill_offset + sizeof(float) * (size_t)a.fill_piece;
+        }
         const int grid = 2 * nb + (a.next_row != nullptr ? a.fill_ctas : 0);
         const int nthreads = nt + (a.next_row != nullptr ? 32 : 0);
         int rc;
@@ -2572,6 +2583,11 @@ static int run_impl(const void* plan, const fbw_b200_summary* summary, const flo
             if (two_step) {
                 ag.next_row  = next_row + i;
                 ag.fill_ctas = idle_sms > 0 ? (idle_sms + i) / nruns : 0;
+                // One filler warp per SM keeps the copy engine busier with few large stores (triphone,
+                // 64 sequences: 2.27 ms per call with 8 KB or 4 KB pieces, 2.40 with 2 KB); several sweep
+                // CTAs, and filler warps, per SM do better with many small ones (BPE-CTC, 256 sequences:
+                // 1.29 ms with 2 KB pieces, 1.34 with 8 KB).
+                ag.fill_piece = 2 * s.B > (i64)sm_count() ? 512 : kFillFloats;
             }
             int rc = launch_group(ag, r.r0, r.r1, r.ms, r.me, r.md, s, r.st, nullptr,
                                   two_step ? (kDoGather | kDoSweep | kDoPost | kDoPatch) : kStages, r.cs);
